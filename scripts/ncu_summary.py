@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Summarise an .ncu-rep: key raw metrics per kernel + top stall instructions from the source page."""
+"""Summarise an .ncu-rep: key raw metrics of the first captured kernel (raw page)."""
 import csv, subprocess, sys, collections
 rep = sys.argv[1]
 raw = subprocess.run(["ncu", "-i", rep, "--page", "raw", "--csv"], capture_output=True, text=True).stdout
@@ -24,20 +24,3 @@ if len(sys.argv) > 2 and sys.argv[2] == "--all":
     r = rows[2]
     for h, u, v in zip(hdr, units, r):
         print(f"{h:90s} {v} {u}")
-src = subprocess.run(["ncu", "-i", rep, "--page", "source", "--csv"], capture_output=True, text=True).stdout
-rows = list(csv.reader(src.splitlines()))
-hdr = None; out = []; k = 0
-for r in rows:
-    if len(r) > 2 and r[0] == "Address":
-        hdr = r; k += 1; continue
-    if hdr is None or len(r) < len(hdr) - 2 or k != 1:
-        continue
-    out.append(dict(zip(hdr, r)))
-tot = sum(int(d["# Samples"]) for d in out)
-print("total samples", tot, "instructions", len(out), "warp-instr executed", sum(int(d["Instructions Executed"]) for d in out))
-stalls = [h for h in hdr if h.startswith("stall_") and "Not Issued" not in h]
-agg = {h: sum(int(d[h]) for d in out) for h in stalls}
-print(sorted(agg.items(), key=lambda x: -x[1])[:8])
-for d in sorted(out, key=lambda d: -int(d["# Samples"]))[:int(sys.argv[3]) if len(sys.argv) > 3 else 25]:
-    s = sorted(((int(d[h]), h) for h in stalls), reverse=True)[:2]
-    print(d["# Samples"], d["Instructions Executed"], d["Source"].strip()[:90], s)

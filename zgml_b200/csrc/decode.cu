@@ -24,7 +24,7 @@
 //
 // CODE SIZE is a first-class constraint here.  The CTAs run in lockstep and every phase's code executes once per layer,
 // so whatever does not fit the instruction caches (L1.5: 32 KB) is re-fetched from L2 by all 148 SMs for every layer:
-// the first version (everything unrolled and inlined per call site, 300 KB of SASS) spent 65 us per layer almost entirely
+// the first version (everything unrolled and inlined per call site, 300 KB of machine code) spent 65 us per layer almost entirely
 // on instruction fetch.  Hence: one call site per routine (a loop over the four matvec phases), loops instead of
 // unrolling wherever latency allows, the chunk producer and the rare paths out of line, descriptor copies by cp.async.
 //

@@ -298,8 +298,8 @@ qgemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             }
             load_rec(slot, j0 + slot + kPf);
-            // Keep the packed values live ACROSS the wait: ptxas otherwise sinks the packs below the wait loop (seen in the
-            // SASS).  A fold of all of them feeds a store that never executes (M is never 2^32 - 1), which pins them here.
+            // Keep the packed values live ACROSS the wait: ptxas otherwise sinks the packs below the wait loop (the
+            // kernel got slower without this).  A fold of all of them feeds a store that never executes (M is never 2^32 - 1), which pins them here.
             uint32_t fold = 0;
 #pragma unroll
             for (int sl = 0; sl < 2; sl++)
