@@ -77,7 +77,15 @@ typedef enum ZgOpTag {
     ZG_OP_GATE = 28,
     ZG_OP_HEAD_LINEAR = 29,
     ZG_OP_POLY_NORM = 30,
-    ZG_OP_END = 31
+    /* Recurrent mixers with an elementwise or scalar decay, and what surrounds them (csrc/recops.cu): the state-space scan
+     * of Mamba-2, the minimal gated recurrent unit, a gated group norm, a per-head RMS norm with a position-dependent
+     * query temperature, and stand-alone activations. */
+    ZG_OP_SSM_SCAN = 31,
+    ZG_OP_MIN_GRU = 32,
+    ZG_OP_GATED_NORM = 33,
+    ZG_OP_HEAD_NORM = 34,
+    ZG_OP_ACTIVATION = 35,
+    ZG_OP_END = 36
 } ZgOpTag;
 
 /* Parameter pack of the sequence-model ops.  buf[] are program buffer indices (ZG_NO_BUF: absent), off[] element offsets,
@@ -89,13 +97,18 @@ typedef enum ZgOpTag {
  * Control buffer `ctl` (int32 words inside an f32 buffer, written by the host before every execution):
  *   [0] position of the step's first token in its sequence, [1] state slot, [ZG_CTL_IDS ..) the step's token ids.
  *
- * EMBED             dst[t, :] = table[ids[t], :] * f0
- *                   buf 0 dst 1 ctl 2 table | off 0 table | n 0 T 1 D 2 wdt | f 0 scale
+ * EMBED             dst[t, :] = table[ids[t], :] * f0; with n3 = 1 a learned position row joins it, unscaled: + positions[p(t), :]
+ *                   (a second table at off 1 of the same arena, p(t) = the token's position in its sequence)
+ *                   buf 0 dst 1 ctl 2 table | off 0 table 1 positions | n 0 T 1 D 2 wdt 3 positions | f 0 scale
  * LINEAR            dst[m, n] = sum_k src[m, k] W[n, k] (+ bias[n])
  *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt
  * NORM              dst = (res +) norm(src) * w ; kind bit 0 clear: (x - mean) / sqrt(var + eps), set: x / sqrt(mean(x^2) + eps);
  *                   kind bit 1: the weight is stored around zero and applied as (1 + w); kind bit 2: the result is also
- *                   multiplied by the gain f1 (a scale of the following product folded into its input)
+ *                   multiplied by the gain f1 (a scale of the following product folded into its input);
+ *                   kind bit 3: Dynamic Tanh instead of a norm, tanh(alpha x) * w + b with no statistics of the row: the bias b
+ *                   (cols values) and the scalar alpha follow w in its arena; kind bit 4: no norm and no weight, the row
+ *                   itself (times the gain with bit 2): dst = res + gain * src, the plain residual step of a pre-norm stack.
+ *                   Bits 3 and 4 combine with a residual and a chained norm, not with the averaged source or the token shift.
  *                   with buf 4: also dst2 = norm(dst) * w2 in the same launch (the norm closing a sublayer and the one opening the next)
  *                   with buf 6 (single-row steps): the last output of the launch then passes a TOKEN_SHIFT (mix at off 2 of the
  *                   arena of the norm it follows, state buf 6, ctl buf 7) in the same launch
@@ -117,8 +130,9 @@ typedef enum ZgOpTag {
  * CAUSAL_CONV       per-channel FIR over time with carried inputs: dst[t, c] = act(sum_j w[c, j] x[t - (taps - 1) + j, c]), x
  *                   before the step taken from the state (external [slots, taps - 1, C], zeros for a fresh slot), which is then
  *                   advanced by the step's inputs.  act 0: none, 1: SiLU.
- *                   buf 0 dst 1 src 2 w [C, taps] 3 state 4 ctl | off 0 w 1 src 2 dst | n 0 T 1 C 2 taps 3 src row stride
- *                   4 dst row stride 5 act 6 wdt
+ *                   With n7 = 1 a bias per channel (off 3 of w's arena) is added before the activation.
+ *                   buf 0 dst 1 src 2 w [C, taps] 3 state 4 ctl | off 0 w 1 src 2 dst 3 bias | n 0 T 1 C 2 taps 3 src row stride
+ *                   4 dst row stride 5 act 6 wdt 7 bias
  * DELTA_RULE        gated delta rule with one decay per head and key channel, state S [dim, vdim] per head (external
  *                   [slots, H, dim, vdim], f32): q, k -> unit vectors (x / sqrt(sum x^2 + f1)), q *= f2; beta = sigmoid(b);
  *                   g = exp(-exp(A_log[h]) * softplus(a + dt_bias)); per token S <- g * S (rows), u = beta * (v - S^T k),
@@ -133,8 +147,12 @@ typedef enum ZgOpTag {
  *                   lowest index); dst[t, c] = {index as int32 bits, s[index]} (weights not renormalised)
  *                   mode 1: z = logits + correction (a bias); the `top` largest z are chosen (ties: lowest index) and weighted
  *                   by the softmax over the chosen z alone
+ *                   mode 2: s = sigmoid(logits); choice scores s + correction; the outputs form n6 equal groups of neighbours, a
+ *                   group scores the sum of its two largest choice scores and only outputs of the n7 best groups can be chosen
+ *                   (n6 <= 1: no groups); the `top` largest choice scores are chosen (ties: lowest index) and weighted by
+ *                   their s divided by (the sum of the chosen s + 1e-20)
  *                   buf 0 dst [T, top, 2] 1 logits 2 correction | off 0 correction 1 logits | n 0 T 1 NE 2 top 3 logits row
- *                   stride 4 wdt 5 mode
+ *                   stride 4 wdt 5 mode 6 groups 7 groups kept
  * MOE_FFN           dst[t] = sum_c weight_c * expert_{index_c}(src[t]); expert e < E: W_down (g * sigmoid(f1 * g) * (u + f2)),
  *                   g = min(W_gate x, f0), u = clamp(W_up x, -f0, f0); index >= E: the identity (x itself).  Expert weights
  *                   are stacked [E, ff, D] (gate, up) and [E, D, ff] (down).
@@ -152,16 +170,20 @@ typedef enum ZgOpTag {
  *                   3 row stride 4 dims 5 layout 6 src head stride 7 src row stride | f 0 base
  * CACHE_APPEND      the step's rows join a per-sequence cache (external [slots, R, width]; position p lives in row p mod R).
  *                   Of the appended columns the first `normed` are RMS-normed with a plain weight (a latent), the next `rot`
- *                   get the token's rotary position (a key part shared by all heads), the rest is copied.
+ *                   get the token's rotary position (a key part shared by all heads), the rest is copied.  With n9 > 0 the
+ *                   normed columns are normed in groups of n9 (key heads), every group with the same weight of n9 values.
  *                   buf 0 cache 1 src 2 ctl 3 norm weight | off 0 src column 1 cache column 2 norm weight
- *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout | f 0 eps 1 rotary base
+ *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout 9 norm group | f 0 eps 1 rotary base
  * CACHED_ATTENTION  softmax attention of the step's queries over cached keys and values.  A query row holds H * maps vectors
  *                   of dk (head h, map m at (h * maps + m) * dk); a key row G * maps vectors of dk; a value row G vectors of
  *                   dv; query (h, m) reads key (h / (H / G), m) and value h / (H / G).  The value cache may be the key cache
  *                   (a latent that serves as both).  Masks: 0 causal, 1 the last `size` positions, 2 causal inside blocks
  *                   of `size` positions counted from position 0.  R must cover what the mask can reach plus the step.
- *                   buf 0 dst [T, H * maps, dv] 1 q 2 key cache 3 value cache 4 ctl
- *                   off 0 q column 1 key column 2 value column (inside a cache row) 3 mask kind 4 mask size
+ *                   With buf 5 a score table [H * maps, off 6] (f32) indexed by the distance i - j is added to the scaled score
+ *                   (any distance bias; a constant per head folds into it).  Weights (off 5): 0 softmax over the visible keys,
+ *                   1 sigmoid(score) of every visible key, not normalised over the keys.
+ *                   buf 0 dst [T, H * maps, dv] 1 q 2 key cache 3 value cache 4 ctl 5 score table
+ *                   off 0 q column 1 key column 2 value column (inside a cache row) 3 mask kind 4 mask size 5 weights 6 table row length
  *                   n 0 T 1 H 2 G 3 maps 4 dk 5 dv 6 q row stride 7 key row width 8 value row width 9 R | f 0 score scale
  * MAP_COMBINE       differential attention's combination of two maps: o = a[.., 0, :] - f0 * a[.., 1, :], then
  *                   o / sqrt(mean(o^2) + f1) * f2 per (token, head)
@@ -174,7 +196,29 @@ typedef enum ZgOpTag {
  *                   n 0 T 1 H 2 N 3 K 4 src head stride 5 src row stride 6 dst head stride 7 dst row stride 8 wdt 9 gate group
  * POLY_NORM         dst[t] = a N(z) + b N(z^2) + c N(z^3) + e with N(v) = v / sqrt(mean(v^2) + f0) over the row, powers taken
  *                   element by element, (a, b, c, e) four weights; may run in place
- *                   buf 0 dst 1 src 2 coefficients | off 0 coefficients | n 0 T 1 columns 2 wdt | f 0 eps */
+ *                   buf 0 dst 1 src 2 coefficients | off 0 coefficients | n 0 T 1 columns 2 wdt | f 0 eps
+ * SSM_SCAN          state-space recurrence with one scalar decay per head and token (Mamba-2): dt = softplus(dt_logit + dt_bias[h]),
+ *                   S <- exp(-exp(A_log[h]) dt) S + dt B x^T (S is N x P per head, f32), y = S^T C + D[h] x.  Head h reads the B and
+ *                   C of group h / (H / G).  x | B | C are columns of one row (the output of the short convolution), the dt
+ *                   logits columns of another.  The state is external [slots, zg_cuda_seq_state_elems(op)] in a layout private
+ *                   to the op, zeros for a fresh slot.
+ *                   buf 0 dst [T, H * P] 1 xbc 2 dt 3 weights 4 state 5 ctl
+ *                   off 0 x 1 B 2 C (columns of an xbc row) 3 dt (column of its row) 4 A_log 5 dt_bias 6 D (weights)
+ *                   n 0 T 1 H 2 G 3 N 4 P 5 xbc row stride 6 dt row stride 7 wdt
+ * MIN_GRU           gated recurrence whose gates read the current token only: z = sigmoid(zl), c = u + 1/2 where u >= 0 and
+ *                   sigmoid(u) where u < 0, S <- (1 - z) S + z c element by element (external [slots, W], zeros for a fresh
+ *                   slot), dst = S * silu(g).  zl | u | g are columns of one row (biases belong to the projection).
+ *                   buf 0 dst 1 proj 2 state 3 ctl | off 0 zl 1 u 2 g (columns) | n 0 T 1 W 2 proj row stride 3 dst row stride
+ * GATED_NORM        dst = N(src * silu(gate)) * w with N an RMS norm over each of n2 equal parts of the row (the gate comes
+ *                   before the norm); may run in place
+ *                   buf 0 dst 1 src 2 gate 3 w | off 0 gate column 1 w | n 0 T 1 columns 2 groups 3 gate row stride 4 wdt
+ *                   5 src row stride 6 dst row stride | f 0 eps
+ * HEAD_NORM         per-head RMS norm in place with one weight of `dim` values shared by the heads, times a temperature that
+ *                   grows with the position p of the token: 1 + f1 * ln(floor((p + 1) / n5) + 1) (n5 = 0: none)
+ *                   buf 0 x 1 w 2 ctl | off 0 column of the first head 1 w | n 0 T 1 heads 2 dim 3 row stride 4 wdt 5 period
+ *                   f 0 eps 1 temperature coefficient
+ * ACTIVATION        dst = act(src) element by element, may run in place; kinds: 0 relu(z)^2, 1 silu, 2 gelu (tanh form), 3 relu
+ *                   buf 0 dst 1 src | n 0 elements 1 kind */
 #define ZG_NO_BUF 0xFFFFFFFFu
 #define ZG_W_F32 0
 #define ZG_W_BF16 1
@@ -518,6 +562,8 @@ size_t zg_cuda_trace_read(ZgCudaCtx* ctx, unsigned long long* host, size_t max_r
 /* f32 slots the scratch operand of a sequence-model op must have (MOE_FFN buf[4]: per-pair activations, or the sorted
  * rows, per-expert tiles and partial products of the grouped tensor-core form); 0 for ops without one. */
 size_t zg_cuda_seq_scratch_elems(const ZgOp* op);
+/* f32 slots per state slot of a sequence-model op that lays out its own state (SSM_SCAN, from H, N and P); 0 otherwise. */
+size_t zg_cuda_seq_state_elems(const ZgOp* op);
 
 void* zg_cuda_malloc(ZgCudaCtx* ctx, size_t bytes);
 void zg_cuda_free_device(ZgCudaCtx* ctx, void* p);

@@ -22,9 +22,13 @@ OP_ALLREDUCE, OP_ALLGATHER = 12, 13   # multi-GPU extensions (need comm_init)
 (OP_EMBED, OP_LINEAR, OP_NORM, OP_WINDOW_ATTENTION, OP_CAUSAL_CONV, OP_DELTA_RULE, OP_ROUTE, OP_MOE_FFN) = range(14, 22)
 (OP_TOKEN_SHIFT, OP_DEPTH_MIX, OP_ROTARY, OP_CACHE_APPEND, OP_CACHED_ATTENTION, OP_MAP_COMBINE, OP_GATE, OP_HEAD_LINEAR,
  OP_POLY_NORM) = range(22, 31)
-OP_END = 31
+(OP_SSM_SCAN, OP_MIN_GRU, OP_GATED_NORM, OP_HEAD_NORM, OP_ACTIVATION) = range(31, 36)
+OP_END = 36
 MASK_CAUSAL, MASK_WINDOW, MASK_BLOCK = 0, 1, 2
 NORM_LAYER, NORM_RMS, NORM_UNIT_OFFSET, NORM_GAIN = 0, 1, 2, 4
+NORM_DYNAMIC_TANH, NORM_NONE = 8, 16       # tanh(alpha x) w + b (bias and alpha follow w); the row itself: no statistics either way
+WEIGHTS_SOFTMAX, WEIGHTS_SIGMOID = 0, 1    # CACHED_ATTENTION: normalised over the visible keys, or sigmoid(score) of each
+ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "relu": 3}
 NO_BUF = 0xFFFFFFFF
 W_F32, W_BF16 = 0, 1
 CTL_POS, CTL_SLOT, CTL_IDS = 0, 1, 8
@@ -208,6 +212,7 @@ SYMBOLS = [
     ("zg_cuda_trace", C.c_int, [vp, C.c_int]),
     ("zg_cuda_trace_read", sz, [vp, vp, sz]),
     ("zg_cuda_seq_scratch_elems", sz, [C.POINTER(ZgOp)]),
+    ("zg_cuda_seq_state_elems", sz, [C.POINTER(ZgOp)]),
     ("zg_cuda_malloc", vp, [vp, sz]),
     ("zg_cuda_free_device", None, [vp, vp]),
     ("zg_cuda_memcpy_h2d", C.c_int, [vp, vp, vp, sz]),

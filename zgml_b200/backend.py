@@ -207,8 +207,9 @@ class DeviceOp:
         return o
 
     @staticmethod
-    def embed(dst, ctl, table, table_off, T, D, scale, wdt):
-        return DeviceOp._seq(abi.OP_EMBED, [dst, ctl, table], [table_off], [T, D, wdt], [scale])
+    def embed(dst, ctl, table, table_off, T, D, scale, wdt, positions_off=None):
+        """Rows of the table times `scale`; with `positions_off` a learned position row of the same arena is added, unscaled."""
+        return DeviceOp._seq(abi.OP_EMBED, [dst, ctl, table], [table_off, positions_off or 0], [T, D, wdt, int(positions_off is not None)], [scale])
 
     @staticmethod
     def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0):
@@ -223,7 +224,16 @@ class DeviceOp:
         result(s); `shift_state` (single-row steps, with `then`) passes `then` through a token shift whose mix lies at shift_off of
         then_w (of w without `then`) and whose carried row is that state buffer.  `average` = (out, coeff_off, terms, stride): the
         row that is normed is sum_j coeff[j] * src[j * stride + .] (coefficients in w's arena), which also goes to buffer `out`."""
-        kinds = {"layer": abi.NORM_LAYER, "rms": abi.NORM_RMS, "rms1": abi.NORM_RMS | abi.NORM_UNIT_OFFSET}
+        kinds = {"layer": abi.NORM_LAYER, "rms": abi.NORM_RMS, "rms1": abi.NORM_RMS | abi.NORM_UNIT_OFFSET,
+                 "dyt": abi.NORM_DYNAMIC_TANH, "none": abi.NORM_NONE}
+        if kind in ("dyt", "none") or (then is not None and then_kind in ("dyt", "none")):
+            # Kinds without row statistics: "dyt" = tanh(alpha x) w + b (bias and alpha follow w in its arena), "none" = the row itself.
+            # The gain belongs to the FIRST norm here (dst = res + gain * f(src), the residual step of a pre-norm stack).
+            assert average is None and shift_state is None
+            g1 = abi.NORM_GAIN if gain is not None else 0
+            return DeviceOp._seq(abi.OP_NORM, [dst, src, None if kind == "none" else w, res, then, then_w if then is not None and then_kind != "none" else None],
+                                 [w_off, then_w_off, 0, dst_off], [rows, cols, kinds[kind] | g1, wdt, kinds[then_kind] if then is not None else 0],
+                                 [eps, gain if gain is not None else 0.0])
         g = abi.NORM_GAIN if gain is not None else 0       # the gain belongs to the last norm of the launch
         fused = shift_state is not None
         if average is not None:
@@ -242,9 +252,9 @@ class DeviceOp:
                              [T, H, G, dim, proj_rs, window, ring_rows], [scale, cap])
 
     @staticmethod
-    def causal_conv(dst, src, w, w_off, state, ctl, T, C, taps, wdt, act="silu", src_off=0, dst_off=0, src_rs=0, dst_rs=0):
-        return DeviceOp._seq(abi.OP_CAUSAL_CONV, [dst, src, w, state, ctl], [w_off, src_off, dst_off],
-                             [T, C, taps, src_rs or C, dst_rs or C, {"none": 0, "silu": 1}[act], wdt])
+    def causal_conv(dst, src, w, w_off, state, ctl, T, C, taps, wdt, act="silu", src_off=0, dst_off=0, src_rs=0, dst_rs=0, bias_off=None):
+        return DeviceOp._seq(abi.OP_CAUSAL_CONV, [dst, src, w, state, ctl], [w_off, src_off, dst_off, bias_off or 0],
+                             [T, C, taps, src_rs or C, dst_rs or C, {"none": 0, "silu": 1}[act], wdt, int(bias_off is not None)])
 
     @staticmethod
     def delta_rule(dst, qkv, beta, a, gate, w, state, ctl, q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off,
@@ -254,11 +264,14 @@ class DeviceOp:
                              [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt], [norm_eps, unit_eps, q_scale])
 
     @staticmethod
-    def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0, mode="corrected_softmax"):
+    def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0, mode="corrected_softmax", groups=0, groups_kept=0):
         """mode "corrected_softmax": softmax over all outputs, choice by softmax + correction, weights not renormalised;
-        "biased_top": choice by logits + bias, weights = softmax over the chosen biased logits."""
+        "biased_top": choice by logits + bias, weights = softmax over the chosen biased logits; "corrected_sigmoid": sigmoid
+        scores, choice by score + correction among the outputs of the `groups_kept` best of `groups` equal groups (a group scores
+        the sum of its two largest choice scores), weights = the chosen scores divided by their sum."""
         return DeviceOp._seq(abi.OP_ROUTE, [dst, logits, w], [corr_off, logits_off],
-                             [T, n_outputs, top, logits_rs or n_outputs, wdt, {"corrected_softmax": 0, "biased_top": 1}[mode]])
+                             [T, n_outputs, top, logits_rs or n_outputs, wdt, {"corrected_softmax": 0, "biased_top": 1, "corrected_sigmoid": 2}[mode],
+                              groups, groups_kept])
 
     @staticmethod
     def moe_ffn(dst, src, route, w, scratch, gate_off, up_off, down_off, T, D, ff, experts, top, wdt, limit, alpha, up_offset=1.0):
@@ -280,15 +293,19 @@ class DeviceOp:
 
     @staticmethod
     def cache_append(cache, src, ctl, src_col, cache_col, T, cols, src_rs, width, rows, norm_w=None, norm_off=0, normed=0, eps=0.0, wdt=0,
-                     rot=0, rot_base=0.0, rot_layout="pairs"):
+                     rot=0, rot_base=0.0, rot_layout="pairs", norm_group=0):
+        """`norm_group` > 0: the normed columns are normed in groups of that many (key heads) sharing one weight of that size."""
         return DeviceOp._seq(abi.OP_CACHE_APPEND, [cache, src, ctl, norm_w if normed else None], [src_col, cache_col, norm_off],
-                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout]], [eps, rot_base])
+                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout], norm_group], [eps, rot_base])
 
     @staticmethod
     def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,
-                         mask="causal", mask_size=0):
+                         mask="causal", mask_size=0, weights="softmax", score_table=None, table_len=0):
+        """`score_table`: an f32 buffer [H * maps, table_len] added to the scaled scores by distance; `weights` "sigmoid": every
+        visible key weighs sigmoid(score), not normalised over the keys."""
         kinds = {"causal": abi.MASK_CAUSAL, "window": abi.MASK_WINDOW, "block": abi.MASK_BLOCK}
-        return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl], [q_col, k_col, v_col, kinds[mask], mask_size],
+        return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl, score_table],
+                             [q_col, k_col, v_col, kinds[mask], mask_size, {"softmax": abi.WEIGHTS_SOFTMAX, "sigmoid": abi.WEIGHTS_SIGMOID}[weights], table_len],
                              [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows], [scale])
 
     @staticmethod
@@ -308,6 +325,27 @@ class DeviceOp:
     @staticmethod
     def poly_norm(dst, src, w, coeff_off, T, cols, eps, wdt):
         return DeviceOp._seq(abi.OP_POLY_NORM, [dst, src, w], [coeff_off], [T, cols, wdt], [eps])
+
+    @staticmethod
+    def ssm_scan(dst, xbc, dt, w, state, ctl, x_col, b_col, c_col, dt_col, a_log_off, dt_bias_off, d_off, T, H, G, N, P, xbc_rs, dt_rs, wdt):
+        return DeviceOp._seq(abi.OP_SSM_SCAN, [dst, xbc, dt, w, state, ctl], [x_col, b_col, c_col, dt_col, a_log_off, dt_bias_off, d_off],
+                             [T, H, G, N, P, xbc_rs, dt_rs, wdt])
+
+    @staticmethod
+    def min_gru(dst, proj, state, ctl, z_col, u_col, g_col, T, W, proj_rs, dst_rs=0):
+        return DeviceOp._seq(abi.OP_MIN_GRU, [dst, proj, state, ctl], [z_col, u_col, g_col], [T, W, proj_rs, dst_rs or W])
+
+    @staticmethod
+    def gated_norm(dst, src, gate, w, w_off, gate_col, T, cols, groups, gate_rs, eps, wdt, src_rs=0, dst_rs=0):
+        return DeviceOp._seq(abi.OP_GATED_NORM, [dst, src, gate, w], [gate_col, w_off], [T, cols, groups, gate_rs, wdt, src_rs or cols, dst_rs or cols], [eps])
+
+    @staticmethod
+    def head_norm(x, w, w_off, ctl, col, T, heads, dim, row_stride, eps, wdt, temp_coef=0.0, temp_every=0):
+        return DeviceOp._seq(abi.OP_HEAD_NORM, [x, w, ctl], [col, w_off], [T, heads, dim, row_stride, wdt, temp_every], [eps, temp_coef])
+
+    @staticmethod
+    def activation(dst, src, n, kind):
+        return DeviceOp._seq(abi.OP_ACTIVATION, [dst, src], [], [n, abi.ACTIVATIONS[kind]])
 
 
 @dataclass
@@ -363,6 +401,11 @@ class ResidentQuantizedWeight:
         q = abi.ZgQWeight()
         q.data, q.rows, q.cols, q.block_size = self.weight.ptr, self.weight.rows, self.weight.cols, abi.QWEIGHT_RESIDENT
         return q
+
+
+def seq_state_elems(op) -> int:
+    """f32 slots per state slot of an op that lays out its own state (zg_cuda_seq_state_elems)."""
+    return int(load_library().zg_cuda_seq_state_elems(C.byref(op)))
 
 
 def seq_scratch_elems(op) -> int:

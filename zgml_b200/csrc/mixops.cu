@@ -65,20 +65,28 @@ __global__ void k_rotary(float* x, const float* src, const float* __restrict__ c
 // A cache row is [normed | rotated | plain]: the first `normed` columns are divided by their root mean square and weighted
 // (a latent), the next `rot` columns get the token's rotary position (a key part shared by the heads), the rest is copied.
 template <typename WT>
-__global__ void k_cache_append(float* __restrict__ cache, const float* __restrict__ src, const float* __restrict__ ctl, const WT* __restrict__ nw,
+__global__ void k_cache_append(float* __restrict__ cache, const float* __restrict__ src, const float* __restrict__ ctl, const WT* __restrict__ nw_,
                                uint32_t cols, uint32_t src_rs, uint32_t width, uint32_t R, uint32_t normed, uint32_t rot, uint32_t layout, float eps,
-                               float base) {
+                               float base, uint32_t norm_group) {
     pdl_enter();
     __shared__ float sh[32];
     const uint32_t t = blockIdx.x;
     const uint32_t pos = (uint32_t)ctl_word(ctl, ZG_CTL_POS) + t, slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
     float* row = cache + ((size_t)slot * R + pos % R) * width;
     const float* s = src + (size_t)t * src_rs;
-    if (normed) {
+    if (normed && norm_group) {                        // key heads: every group of norm_group columns by its own root mean square, one warp each
+        const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        for (uint32_t g0 = warp * norm_group; g0 < normed; g0 += nw * norm_group) {
+            float q = 0.0f;
+            for (uint32_t c = lane; c < norm_group; c += 32) q = fmaf(s[g0 + c], s[g0 + c], q);
+            const float inv = 1.0f / sqrtf(warp_sum(q) / (float)norm_group + eps);
+            for (uint32_t c = lane; c < norm_group; c += 32) row[g0 + c] = s[g0 + c] * inv * wld(nw_, c);
+        }
+    } else if (normed) {
         float q = 0.0f;
         for (uint32_t c = threadIdx.x; c < normed; c += blockDim.x) q = fmaf(s[c], s[c], q);
         const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)normed + eps);
-        for (uint32_t c = threadIdx.x; c < normed; c += blockDim.x) row[c] = s[c] * inv * wld(nw, c);
+        for (uint32_t c = threadIdx.x; c < normed; c += blockDim.x) row[c] = s[c] * inv * wld(nw_, c);
     }
     const uint32_t half = rot / 2;
     for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
@@ -103,7 +111,11 @@ struct CaArgs {
     float* dst; const float* q; const float* kc; const float* vc; const float* ctl;
     uint32_t T, H, G, maps, dk, dv, q_rs, q_off, kw, k_off, vw, v_off, R, kind, size;
     float scale;
+    const float* tab;      // score table [H * maps, tab_rs] by distance, or null
+    uint32_t tab_rs, wkind;   // weights: 0 softmax over the visible keys, 1 sigmoid of every visible key (not normalised)
 };
+// weight of a visible key under the unnormalised kind
+__device__ __forceinline__ float ca_sigmoid(float s) { return __frcp_rn(1.0f + expf(-s)); }
 constexpr int kCaMaxDv = 1024;   // 32 channels per lane in the per-query kernel
 // Any shape: one warp per (token, head, map); 32 keys at a time, lane = key for the scores, lane = channel for the sum.
 __global__ void k_cached_attention(CaArgs a) {
@@ -134,12 +146,17 @@ __global__ void k_cached_attention(CaArgs a) {
             float d = 0.0f;
             for (uint32_t c = 0; c < a.dk; c++) d = fmaf(q[c], k[c], d);
             s = d * a.scale;
+            if (a.tab) s += a.tab[(size_t)hm * a.tab_rs + (p - j)];
         }
-        const float m_new = fmaxf(mx, warp_max(s));    // finite: key j0 is visible
-        const float corr = expf(mx - m_new);
-        const float e = j <= p ? expf(s - m_new) : 0.0f;
-        l = l * corr + warp_sum(e);
-        mx = m_new;
+        float corr = 1.0f, e;
+        if (a.wkind) e = j <= p ? ca_sigmoid(s) : 0.0f;
+        else {
+            const float m_new = fmaxf(mx, warp_max(s));    // finite: key j0 is visible
+            corr = expf(mx - m_new);
+            e = j <= p ? expf(s - m_new) : 0.0f;
+            l = l * corr + warp_sum(e);
+            mx = m_new;
+        }
         const uint32_t cnt = min(32u, p - j0 + 1);
 #pragma unroll
         for (int i = 0; i < kCaMaxDv / 32; i++) acc[i] *= corr;
@@ -153,7 +170,7 @@ __global__ void k_cached_attention(CaArgs a) {
             }
         }
     }
-    const float inv = 1.0f / l;
+    const float inv = a.wkind ? 1.0f : 1.0f / l;
     float* out = a.dst + ((size_t)t * HM + hm) * a.dv;
 #pragma unroll
     for (int i = 0; i < kCaMaxDv / 32; i++) {
@@ -208,12 +225,14 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
     const uint32_t v_cols = min((uint32_t)DV, a.dv - vs * DV);
     uint32_t p_r[4], lo_r[4];
     bool ok_r[4];
+    const float* tab_r[4];                             // the row's line of the score table, so that tab_r[p - j] is the entry of key j
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const uint32_t r = r0 + 4 * ty + i;
         ok_r[i] = r < total;
         p_r[i] = pos0 + (ok_r[i] ? r / rh : 0);
         lo_r[i] = mask_low(p_r[i], a.kind, a.size);
+        tab_r[i] = a.tab ? a.tab + (size_t)((g * rh + (ok_r[i] ? r % rh : 0)) * a.maps + m) * a.tab_rs : nullptr;
     }
     auto load_q = [&](uint32_t d0, uint32_t stage) {
         for (uint32_t i = tid; i < kCtBQ * (kCtDS / 4); i += kCtThreads) {
@@ -300,9 +319,16 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
 #pragma unroll
             for (int c = 0; c < 4; c++) {
                 const uint32_t j = s0 + tx + 16 * c;
-                const float sv = (ok_r[r] && j <= p_r[r] && j >= lo_r[r] && j < k_end) ? sc[r][c] * a.scale : -INFINITY;
+                const bool seen = ok_r[r] && j <= p_r[r] && j >= lo_r[r] && j < k_end;
+                float sv = seen ? sc[r][c] * a.scale : -INFINITY;
+                if (seen && tab_r[r]) sv += tab_r[r][p_r[r] - j];
                 sc[r][c] = sv;
                 rmax = fmaxf(rmax, sv);
+            }
+            if (a.wkind) {                             // every visible key weighs sigmoid(score): no running maximum, no sum
+#pragma unroll
+                for (int c = 0; c < 4; c++) Ps[row * PP + tx + 16 * c] = sc[r][c] == -INFINITY ? 0.0f : ca_sigmoid(sc[r][c]);
+                continue;
             }
 #pragma unroll
             for (int off = 8; off > 0; off >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, off));
@@ -342,7 +368,7 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
         if (!ok_r[r]) continue;
         const uint32_t hm = (g * rh + row % rh) * a.maps + m;
         if (splits == 1) {
-            const float inv = 1.0f / l_run[r];         // every query sees itself
+            const float inv = a.wkind ? 1.0f : 1.0f / l_run[r];         // every query sees itself
             float* out = a.dst + ((size_t)(row / rh) * a.H * a.maps + hm) * a.dv + (size_t)vs * DV;
 #pragma unroll
             for (int c = 0; c < OC; c++) if (tx + 16 * c < v_cols) out[tx + 16 * c] = o[r][c] * inv;
@@ -356,11 +382,14 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
 }
 // merge of the key shares: CTA (x, y) = 128 value columns y of (token, head, map) x; a share that saw no key carries
 // max = -inf and weighs nothing (its output is zero)
-__global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits) {
+__global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits,
+                                                                uint32_t wkind) {
     pdl_enter();
     __shared__ float w[kCtMaxSplits];
     const float* P = part + (size_t)blockIdx.x * splits * (4 + dv);
-    if (threadIdx.x < 32) {                            // warp 0: the shares' weights exp(m_i - M) / L
+    if (wkind) {                                       // unnormalised weights: the shares just add up
+        if (threadIdx.x < splits) w[threadIdx.x] = 1.0f;
+    } else if (threadIdx.x < 32) {                            // warp 0: the shares' weights exp(m_i - M) / L
         float m0 = threadIdx.x < splits ? P[threadIdx.x * (4 + dv)] : -INFINITY, m1 = threadIdx.x + 32 < splits ? P[(threadIdx.x + 32) * (4 + dv)] : -INFINITY;
         float l0 = threadIdx.x < splits ? P[threadIdx.x * (4 + dv) + 1] : 0.0f, l1 = threadIdx.x + 32 < splits ? P[(threadIdx.x + 32) * (4 + dv) + 1] : 0.0f;
         const float M = warp_max(fmaxf(m0, m1));
@@ -410,6 +439,7 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
     const float* vbase = a.vc + (size_t)slot * a.R * a.vw + a.v_off + (size_t)g * a.dv;
     const bool ok = row < total;
     const uint32_t p_r = pos0 + (ok ? row / rh : 0), lo_r = mask_low(p_r, a.kind, a.size);
+    const float* tab_r = a.tab ? a.tab + (size_t)((g * rh + (ok ? row % rh : 0)) * a.maps + m) * a.tab_rs : nullptr;
     const uint32_t dk4 = a.dk / 4, dv4 = a.dv / 4;
     const uint32_t chunk4 = (dk4 + kCfParts - 1) / kCfParts, d_begin = 4 * min(dk4, warp * chunk4), d_end = 4 * min(dk4, (warp + 1) * chunk4);
     for (uint32_t i = tid; i < kCfRows * dk4; i += kCfThreads) {     // rows past the step's are zero: their scores are never used
@@ -470,17 +500,19 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
             float d = 0.0f;
 #pragma unroll
             for (int w = 0; w < kCfParts; w++) d += Sp[(w * kCfRows + row) * kCfKeys + kk];
-            sv[u] = (ok && kk < nk && j <= p_r && j >= lo_r) ? d * a.scale : -INFINITY;
+            const bool seen = ok && kk < nk && j <= p_r && j >= lo_r;
+            sv[u] = seen ? d * a.scale : -INFINITY;
+            if (seen && tab_r) sv[u] += tab_r[p_r - j];
         }
         float rmax = fmaxf(sv[0], sv[1]);
 #pragma unroll
         for (int off = 8; off > 0; off >>= 1) rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, off));
-        const float new_m = fmaxf(m_run, rmax);
-        const float alpha = m_run == -INFINITY ? (new_m == -INFINITY ? 1.0f : 0.0f) : expf(m_run - new_m);
+        const float new_m = a.wkind ? 0.0f : fmaxf(m_run, rmax);
+        const float alpha = a.wkind ? 1.0f : (m_run == -INFINITY ? (new_m == -INFINITY ? 1.0f : 0.0f) : expf(m_run - new_m));
         float rsum = 0.0f;
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-            const float pv = sv[u] == -INFINITY ? 0.0f : expf(sv[u] - new_m);
+            const float pv = sv[u] == -INFINITY ? 0.0f : (a.wkind ? ca_sigmoid(sv[u]) : expf(sv[u] - new_m));
             Ss[row * kCfKeys + kq + 16 * u] = pv;
             rsum += pv;
         }
@@ -512,7 +544,7 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
         }
     }
     __syncthreads();
-    if (kq == 0) Al[row] = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    if (kq == 0) Al[row] = a.wkind ? 1.0f : (l_run > 0.0f ? 1.0f / l_run : 0.0f);
     if (splits > 1 && kq == 0 && ok) {
         float* mine = part + (((size_t)(row / rh) * a.H * a.maps + (g * rh + row % rh) * a.maps + m) * splits + blockIdx.y) * (4 + a.dv);
         mine[0] = m_run; mine[1] = l_run;
@@ -752,7 +784,8 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             const size_t normed = s.n[5], rot = s.n[6];
             if (!T || !cols || R < T || s.off[0] + cols > srs || s.off[1] + cols > width || normed + rot > cols || rot % 2 || s.n[8] > 1) return fail("cache_append: shape");
             if (!have(0) || elems[s.buf[0]] < R * width || !fits(1, 0, (T - 1) * srs + s.off[0] + cols) || !fits(2, 0, ZG_CTL_IDS)) return fail("cache_append: extent");
-            if (normed && !wfits(3, s.n[7], s.off[2], normed)) return fail("cache_append: norm weight");
+            if (normed && s.n[9] && normed % s.n[9]) return fail("cache_append: norm groups");
+            if (normed && !wfits(3, s.n[7], s.off[2], s.n[9] ? s.n[9] : normed)) return fail("cache_append: norm weight");
             if (rot && !(s.f[1] > 0.0f)) return fail("cache_append: rotary base");
             return true;
         }
@@ -766,6 +799,11 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
                 elems[s.buf[3]] < R * vw || !fits(4, 0, ZG_CTL_IDS))
                 return fail("cached_attention: extent");
             if (s.buf[0] == s.buf[1]) return fail("cached_attention: in place");
+            if (s.off[5] > 1) return fail("cached_attention: weights");
+            if (s.buf[5] != ZG_NO_BUF) {               // the table must cover every distance the mask lets a query reach
+                const size_t reach = kind == 0 ? R : (size < R ? size : R);
+                if (s.off[6] < reach || !fits(5, 0, H * maps * (size_t)s.off[6])) return fail("cached_attention: score table");
+            }
             return true;
         }
         case ZG_OP_MAP_COMBINE: {
@@ -839,7 +877,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
         }
         case ZG_OP_CACHE_APPEND:
             ZG_SEQ_WDT(s.n[5] ? s.n[7] : ZG_W_F32, launch_pdl(k_cache_append<WT>, dim3(s.n[0]), dim3(128), 0, st, bufs[s.buf[0]] + s.off[1], bufs[s.buf[1]] + s.off[0], bufs[s.buf[2]],
-                                                             s.n[5] ? wptr<WT>(bufs, s.buf[3], s.off[2]) : nullptr, s.n[1], s.n[2], s.n[3], s.n[4], s.n[5], s.n[6], s.n[8], s.f[0], s.f[1]));
+                                                             s.n[5] ? wptr<WT>(bufs, s.buf[3], s.off[2]) : nullptr, s.n[1], s.n[2], s.n[3], s.n[4], s.n[5], s.n[6], s.n[8], s.f[0], s.f[1], s.n[9]));
             ZG_SEQ_CHECK();
             return true;
         case ZG_OP_CACHED_ATTENTION: {
@@ -847,6 +885,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.dst = bufs[s.buf[0]]; a.q = bufs[s.buf[1]]; a.kc = bufs[s.buf[2]]; a.vc = bufs[s.buf[3]]; a.ctl = bufs[s.buf[4]];
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.maps = s.n[3]; a.dk = s.n[4]; a.dv = s.n[5]; a.q_rs = s.n[6]; a.q_off = s.off[0];
             a.kw = s.n[7]; a.k_off = s.off[1]; a.vw = s.n[8]; a.v_off = s.off[2]; a.R = s.n[9]; a.kind = s.off[3]; a.size = s.off[4]; a.scale = s.f[0];
+            a.tab = s.buf[5] != ZG_NO_BUF ? bufs[s.buf[5]] : nullptr; a.tab_rs = s.off[6]; a.wkind = s.off[5];
             const bool aligned = ca_aligned(s) && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
             if (aligned && ca_few(s)) {
                 const uint32_t S = scratch ? ca_splits(s) : 1, alias = cf_alias(s) ? 1u : 0u;
@@ -863,7 +902,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
 #undef ZG_CF
                 if (S > 1) {
                     ZG_SEQ_CHECK();
-                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S);
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S, a.wkind);
                 }
             } else if (aligned) {
                 const uint32_t S = scratch ? ca_splits(s) : 1;
@@ -884,7 +923,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
                 }
                 if (S > 1) {
                     ZG_SEQ_CHECK();
-                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S);
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S, a.wkind);
                 }
             } else {
                 const uint32_t warps = 4, items = a.T * a.H * a.maps;

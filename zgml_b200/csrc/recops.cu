@@ -1,0 +1,316 @@
+// Sequence-model DeviceOps ZG_OP_SSM_SCAN .. ZG_OP_ACTIVATION (parameter packs in include/zgml_cuda.h): recurrent mixers
+// whose decay is a scalar per head (the state-space scan of Mamba-2) or a gate per element (the minimal gated recurrent
+// unit), the gated group norm that closes the former, a per-head RMS norm with a position-dependent temperature, and
+// stand-alone activations.  Everything here is f32: step sizes, softplus and exponentials, decays, gates, the states and
+// their read-outs, norms and positions.
+#include "seq_common.cuh"
+
+#include <math.h>
+
+namespace {
+
+// ── SSM_SCAN ─────────────────────────────────────────────────────────────────────────────────────────────────────
+// Columns of a head's state S [N, P] evolve independently given the token's B, C, decay and step size, so a head is split by
+// columns over CTAs.  A thread keeps kSsmRows state rows of one column in registers; the NS threads of a column sit in
+// adjacent lanes (NS a power of two <= 32) and meet by shuffles for the read-out.  Thread s of a column owns rows
+// 4 s + 4 NS q + i (q < 2, i < 4): the NS lanes read consecutive float4s of B and C from shared memory.  Per token the
+// critical path is one FMA per state element: S = a S + (dt x) B; the read-out sum hangs off it.
+// The per-token operands of a tile of tokens (B, C, the CTA's x columns, dt and the decay) are staged in shared memory by
+// the whole CTA; two tiles are in flight, so the next tile's loads run under this tile's walk.
+// State in memory: [H][column blocks][kSsmRows][kSsmThreads], element (i, thread) — each thread's rows, fully coalesced;
+// the layout is private to the op (zeros mean an empty state in any layout).
+constexpr int kSsmRows = 8, kSsmThreads = 128, kSsmTile = 16, kSsmMaxN = kSsmRows * 32;
+__host__ __device__ inline uint32_t ssm_slices(uint32_t N) {
+    uint32_t ns = 1;
+    while (ns * kSsmRows < N) ns <<= 1;
+    return ns;
+}
+struct SsmArgs {
+    float* dst; const float* xbc; const float* dtl; float* state; const float* ctl;
+    uint32_t T, H, G, N, P, x_off, b_off, c_off, dt_off, xbc_rs, dt_rs;
+};
+template <typename WT, uint32_t NS>
+__global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* __restrict__ a_log, const WT* __restrict__ dt_bias, const WT* __restrict__ dskip) {
+    pdl_enter();
+    constexpr uint32_t CP = kSsmThreads / NS, NP = NS * kSsmRows;     // columns per CTA, padded state rows
+    extern __shared__ __align__(16) float sm[];
+    // per stage: B [tile][NP], C [tile][NP], x [tile][CP], dt [tile], decay [tile]
+    constexpr uint32_t kStage = kSsmTile * (2 * NP + CP + 2);
+    const uint32_t tid = threadIdx.x, s = tid % NS, pl = tid / NS;
+    const uint32_t h = blockIdx.y, cb = blockIdx.x, g = h / (a.H / a.G);
+    const uint32_t p = cb * CP + pl;
+    const bool col_ok = p < a.P;
+    const uint32_t slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
+    const uint32_t n_cb = (a.P + CP - 1) / CP;
+    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (kSsmRows * kSsmThreads);
+    float S[kSsmRows];
+#pragma unroll
+    for (int i = 0; i < kSsmRows; i++) S[i] = st[i * kSsmThreads + tid];
+    const float neg_a = -expf(wld(a_log, h)), bias = wld(dt_bias, h), dsk = wld(dskip, h);
+
+    auto stage_tile = [&](uint32_t t0, uint32_t stage) {
+        float* Bs = sm + stage * kStage;
+        float* Cs = Bs + kSsmTile * NP;
+        float* Xs = Cs + kSsmTile * NP;
+        float* Ds = Xs + kSsmTile * CP;
+        float* As = Ds + kSsmTile;
+        const uint32_t nt = min((uint32_t)kSsmTile, a.T - t0);
+        for (uint32_t e = tid; e < nt * NP; e += kSsmThreads) {
+            const uint32_t tt = e / NP, n = e % NP;
+            const float* row = a.xbc + (size_t)(t0 + tt) * a.xbc_rs + (size_t)g * a.N;
+            Bs[e] = n < a.N ? row[a.b_off + n] : 0.0f;
+            Cs[e] = n < a.N ? row[a.c_off + n] : 0.0f;
+        }
+        for (uint32_t e = tid; e < nt * CP; e += kSsmThreads) {
+            const uint32_t tt = e / CP, c = cb * CP + e % CP;
+            Xs[e] = c < a.P ? a.xbc[(size_t)(t0 + tt) * a.xbc_rs + a.x_off + (size_t)h * a.P + c] : 0.0f;
+        }
+        if (tid < nt) {
+            const float dt = softplusf_(a.dtl[(size_t)(t0 + tid) * a.dt_rs + a.dt_off + h] + bias);
+            Ds[tid] = dt;
+            As[tid] = expf(neg_a * dt);
+        }
+    };
+    for (uint32_t t0 = 0, it = 0; t0 < a.T; t0 += kSsmTile, it++) {
+        const uint32_t stage = it & 1;
+        stage_tile(t0, stage);                          // the other stage may still be read by slower warps: two stages, one barrier
+        __syncthreads();
+        const float* Bs = sm + stage * kStage;
+        const float* Cs = Bs + kSsmTile * NP;
+        const float* Xs = Cs + kSsmTile * NP;
+        const float* Ds = Xs + kSsmTile * CP;
+        const float* As = Ds + kSsmTile;
+        const uint32_t nt = min((uint32_t)kSsmTile, a.T - t0);
+        for (uint32_t tt = 0; tt < nt; tt++) {
+            const float x = Xs[tt * CP + pl], dec = As[tt], dtx = Ds[tt] * x;
+            float y = 0.0f;
+#pragma unroll
+            for (int q = 0; q < kSsmRows / 4; q++) {
+                const float4 b = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * (s + NS * q));
+                const float4 c = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * (s + NS * q));
+                S[4 * q + 0] = fmaf(dec, S[4 * q + 0], dtx * b.x);
+                S[4 * q + 1] = fmaf(dec, S[4 * q + 1], dtx * b.y);
+                S[4 * q + 2] = fmaf(dec, S[4 * q + 2], dtx * b.z);
+                S[4 * q + 3] = fmaf(dec, S[4 * q + 3], dtx * b.w);
+                y = fmaf(S[4 * q + 0], c.x, fmaf(S[4 * q + 1], c.y, fmaf(S[4 * q + 2], c.z, fmaf(S[4 * q + 3], c.w, y))));
+            }
+#pragma unroll
+            for (uint32_t o = NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (s == 0 && col_ok) a.dst[(size_t)(t0 + tt) * a.H * a.P + (size_t)h * a.P + p] = fmaf(dsk, x, y);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kSsmRows; i++) st[i * kSsmThreads + tid] = S[i];
+}
+static size_t ssm_state_elems(uint32_t H, uint32_t N, uint32_t P) {
+    const uint32_t CP = kSsmThreads / ssm_slices(N);
+    return (size_t)H * ((P + CP - 1) / CP) * kSsmRows * kSsmThreads;
+}
+
+// ── MIN_GRU: one thread per channel, the tokens walked in order ──────────────────────────────────────────────────
+// The gate and the candidate of a token do not depend on the state, so four tokens' worth are evaluated ahead of the chain
+// S <- S + z (c - S), which is all that is serial.
+__global__ void k_min_gru(float* __restrict__ dst, const float* __restrict__ proj, float* __restrict__ state, const float* __restrict__ ctl,
+                          uint32_t T, uint32_t W, uint32_t rs, uint32_t drs, uint32_t z_off, uint32_t u_off, uint32_t g_off) {
+    pdl_enter();
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * W;
+    float S = st[c];
+    for (uint32_t t0 = 0; t0 < T; t0 += 4) {
+        float z[4], cand[4], gate[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (t0 + i < T) {
+                const float* row = proj + (size_t)(t0 + i) * rs;
+                const float u = row[u_off + c], gl = row[g_off + c];
+                z[i] = sigmoidf_(row[z_off + c]);
+                cand[i] = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
+                gate[i] = gl * sigmoidf_(gl);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (t0 + i < T) {
+                S = fmaf(z[i], cand[i], (1.0f - z[i]) * S);
+                dst[(size_t)(t0 + i) * drs + c] = S * gate[i];
+            }
+        }
+    }
+    st[c] = S;
+}
+
+// ── GATED_NORM: one warp per (token, group) ──────────────────────────────────────────────────────────────────────
+template <typename WT>
+__global__ void k_gated_norm(float* dst, const float* src, const float* __restrict__ gate, const WT* __restrict__ w, uint32_t T, uint32_t cols,
+                             uint32_t groups, uint32_t gate_rs, uint32_t src_rs, uint32_t dst_rs, float eps) {
+    pdl_enter();
+    const uint32_t item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= T * groups) return;
+    const uint32_t t = item / groups, gi = item % groups, gs = cols / groups, c0 = gi * gs;
+    const float* x = src + (size_t)t * src_rs + c0;
+    const float* gt = gate + (size_t)t * gate_rs + c0;
+    float q = 0.0f;
+    for (uint32_t c = lane; c < gs; c += 32) {
+        const float z = gt[c], v = x[c] * (z * sigmoidf_(z));
+        q = fmaf(v, v, q);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)gs + eps);
+    float* out = dst + (size_t)t * dst_rs + c0;
+    for (uint32_t c = lane; c < gs; c += 32) {
+        const float z = gt[c], v = x[c] * (z * sigmoidf_(z));
+        out[c] = v * inv * wld(w, c0 + c);
+    }
+}
+
+// ── HEAD_NORM: one warp per (token, head), in place ──────────────────────────────────────────────────────────────
+template <typename WT>
+__global__ void k_head_norm(float* x, const WT* __restrict__ w, const float* __restrict__ ctl, uint32_t T, uint32_t heads, uint32_t dim, uint32_t rs,
+                            uint32_t period, float eps, float coef) {
+    pdl_enter();
+    const uint32_t item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= T * heads) return;
+    const uint32_t t = item / heads, hd = item % heads;
+    float* v = x + (size_t)t * rs + (size_t)hd * dim;
+    float q = 0.0f;
+    for (uint32_t c = lane; c < dim; c += 32) q = fmaf(v[c], v[c], q);
+    float mult = 1.0f / sqrtf(warp_sum(q) / (float)dim + eps);
+    if (period) {
+        const uint32_t pos = (uint32_t)ctl_word(ctl, ZG_CTL_POS) + t;
+        mult *= fmaf(coef, logf((float)((pos + 1) / period) + 1.0f), 1.0f);
+    }
+    for (uint32_t c = lane; c < dim; c += 32) v[c] = v[c] * wld(w, c) * mult;
+}
+
+// ── ACTIVATION ───────────────────────────────────────────────────────────────────────────────────────────────────
+__global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t kind) {
+    pdl_enter();
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    const float z = src[e];
+    float y;
+    switch (kind) {
+        case 0: { const float r = fmaxf(z, 0.0f); y = r * r; break; }
+        case 1: y = z * sigmoidf_(z); break;
+        case 2: y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z))); break;
+        default: y = fmaxf(z, 0.0f); break;
+    }
+    dst[e] = y;
+}
+
+}  // namespace
+
+// f32 slots per state slot of an op whose state layout is its own (SSM_SCAN); 0 for every other op
+extern "C" __attribute__((visibility("default"))) size_t zg_cuda_seq_state_elems(const ZgOp* op) {
+    if (!op || op->tag != ZG_OP_SSM_SCAN) return 0;
+    const ZgSeqOp& s = op->u.seq;
+    if (!s.n[1] || !s.n[3] || !s.n[4] || s.n[3] > (uint32_t)kSsmMaxN) return 0;
+    return ssm_state_elems(s.n[1], s.n[3], s.n[4]);
+}
+
+bool zg_rec_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n) {
+    const ZgSeqOp& s = op.u.seq;
+    auto fail = [&](const char* m) { snprintf(why, why_n, "%s", m); return false; };
+    auto have = [&](int i) { return s.buf[i] != ZG_NO_BUF && s.buf[i] < n_bufs; };
+    auto fits = [&](int i, size_t off, size_t n) { return have(i) && off + n <= elems[s.buf[i]]; };
+    auto wfits = [&](int i, uint32_t wdt, size_t off, size_t n) { return wdt <= ZG_W_BF16 && have(i) && (wdt == ZG_W_BF16 ? (off + n + 1) / 2 : off + n) <= elems[s.buf[i]]; };
+    switch (op.tag) {
+        case ZG_OP_SSM_SCAN: {
+            const size_t T = s.n[0], H = s.n[1], G = s.n[2], N = s.n[3], P = s.n[4], xrs = s.n[5], drs = s.n[6];
+            if (!T || !H || !G || H % G || !N || N > (size_t)kSsmMaxN || !P) return fail("ssm_scan: shape");
+            if (s.off[0] + H * P > xrs || s.off[1] + G * N > xrs || s.off[2] + G * N > xrs || s.off[3] + H > drs) return fail("ssm_scan: columns");
+            if (!fits(0, 0, T * H * P) || !fits(1, 0, T * xrs) || !fits(2, 0, T * drs) || !wfits(3, s.n[7], s.off[4], H) || !wfits(3, s.n[7], s.off[5], H) ||
+                !wfits(3, s.n[7], s.off[6], H) || !have(4) || elems[s.buf[4]] < ssm_state_elems((uint32_t)H, (uint32_t)N, (uint32_t)P) || !fits(5, 0, ZG_CTL_IDS))
+                return fail("ssm_scan: extent");
+            if (s.buf[0] == s.buf[1] || s.buf[0] == s.buf[2]) return fail("ssm_scan: in place");
+            return true;
+        }
+        case ZG_OP_MIN_GRU: {
+            const size_t T = s.n[0], W = s.n[1], rs = s.n[2], drs = s.n[3];
+            if (!T || !W || drs < W || s.off[0] + W > rs || s.off[1] + W > rs || s.off[2] + W > rs) return fail("min_gru: shape");
+            if (!fits(0, 0, (T - 1) * drs + W) || !fits(1, 0, T * rs) || !have(2) || elems[s.buf[2]] < W || !fits(3, 0, ZG_CTL_IDS)) return fail("min_gru: extent");
+            if (s.buf[0] == s.buf[1]) return fail("min_gru: in place");
+            return true;
+        }
+        case ZG_OP_GATED_NORM: {
+            const size_t T = s.n[0], cols = s.n[1], groups = s.n[2], grs = s.n[3], srs = s.n[5], drs = s.n[6];
+            if (!T || !cols || !groups || cols % groups || srs < cols || drs < cols || s.off[0] + cols > grs) return fail("gated_norm: shape");
+            if (!fits(0, 0, (T - 1) * drs + cols) || !fits(1, 0, (T - 1) * srs + cols) || !fits(2, 0, (T - 1) * grs + s.off[0] + cols) || !wfits(3, s.n[4], s.off[1], cols))
+                return fail("gated_norm: extent");
+            return true;
+        }
+        case ZG_OP_HEAD_NORM: {
+            const size_t T = s.n[0], heads = s.n[1], dim = s.n[2], rs = s.n[3];
+            if (!T || !heads || !dim || s.off[0] + heads * dim > rs) return fail("head_norm: shape");
+            if (!fits(0, 0, (T - 1) * rs + s.off[0] + heads * dim) || !wfits(1, s.n[4], s.off[1], dim) || !fits(2, 0, ZG_CTL_IDS)) return fail("head_norm: extent");
+            return true;
+        }
+        case ZG_OP_ACTIVATION: {
+            if (!s.n[0] || s.n[1] > 3) return fail("activation: shape");
+            if (!fits(0, 0, s.n[0]) || !fits(1, 0, s.n[0])) return fail("activation: extent");
+            return true;
+        }
+        default: return fail("not a sequence op");
+    }
+}
+
+uint32_t zg_rec_op_writes(uint32_t tag) {
+    switch (tag) {
+        case ZG_OP_SSM_SCAN: return 1u | (1u << 4);
+        case ZG_OP_MIN_GRU: return 1u | (1u << 2);
+        default: return 1u;
+    }
+}
+
+bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
+    const ZgSeqOp& s = op.u.seq;
+    switch (op.tag) {
+        case ZG_OP_SSM_SCAN: {
+            SsmArgs a;
+            a.dst = bufs[s.buf[0]]; a.xbc = bufs[s.buf[1]]; a.dtl = bufs[s.buf[2]]; a.state = bufs[s.buf[4]]; a.ctl = bufs[s.buf[5]];
+            a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.N = s.n[3]; a.P = s.n[4]; a.x_off = s.off[0]; a.b_off = s.off[1]; a.c_off = s.off[2]; a.dt_off = s.off[3];
+            a.xbc_rs = s.n[5]; a.dt_rs = s.n[6];
+            const uint32_t NS = ssm_slices(a.N), CP = kSsmThreads / NS;
+            const dim3 grid((a.P + CP - 1) / CP, a.H);
+            const size_t smem = (size_t)2 * kSsmTile * (2 * NS * kSsmRows + CP + 2) * sizeof(float);
+#define ZG_SSM(NS_)                                                                                                                       \
+    case NS_:                                                                                                                             \
+        ZG_SEQ_WDT(s.n[7], {                                                                                                              \
+            if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+            launch_pdl(k_ssm_scan<WT, NS_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
+                       wptr<WT>(bufs, s.buf[3], s.off[6]));                                                                               \
+        });                                                                                                                               \
+        break;
+            switch (NS) { ZG_SSM(1) ZG_SSM(2) ZG_SSM(4) ZG_SSM(8) ZG_SSM(16) default: ZG_SSM(32) }
+#undef ZG_SSM
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_MIN_GRU:
+            launch_pdl(k_min_gru, dim3((s.n[1] + 63) / 64), dim3(64), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], s.n[0], s.n[1], s.n[2], s.n[3],
+                       s.off[0], s.off[1], s.off[2]);
+            ZG_SEQ_CHECK();
+            return true;
+        case ZG_OP_GATED_NORM: {
+            const uint32_t items = s.n[0] * s.n[2];
+            ZG_SEQ_WDT(s.n[4], launch_pdl(k_gated_norm<WT>, dim3((items + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]] + s.off[0], wptr<WT>(bufs, s.buf[3], s.off[1]),
+                                          s.n[0], s.n[1], s.n[2], s.n[3], s.n[5], s.n[6], s.f[0]));
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_HEAD_NORM: {
+            const uint32_t items = s.n[0] * s.n[1];
+            ZG_SEQ_WDT(s.n[4], launch_pdl(k_head_norm<WT>, dim3((items + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]] + s.off[0], wptr<WT>(bufs, s.buf[1], s.off[1]), bufs[s.buf[2]], s.n[0], s.n[1],
+                                          s.n[2], s.n[3], s.n[5], s.f[0], s.f[1]));
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_ACTIVATION:
+            launch_pdl(k_activation, dim3((s.n[0] + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], s.n[0], s.n[1]);
+            ZG_SEQ_CHECK();
+            return true;
+        default:
+            zg_set_error("unsupported sequence op tag %u", op.tag);
+            return false;
+    }
+}

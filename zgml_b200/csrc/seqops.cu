@@ -14,10 +14,16 @@ namespace {
 
 // ── EMBED ─────────────────────────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
-__global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, const WT* __restrict__ table, uint32_t D, float scale) {
+__global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, const WT* __restrict__ table, uint32_t D, float scale,
+                        const WT* __restrict__ positions) {
     pdl_enter();
     const uint32_t t = blockIdx.x;
     const size_t row = (size_t)ctl_word(ctl, ZG_CTL_IDS + t) * D;
+    if (positions) {       // a learned position row, not scaled
+        const size_t prow = ((size_t)ctl_word(ctl, ZG_CTL_POS) + t) * D;
+        for (uint32_t c = threadIdx.x; c < D; c += blockDim.x) dst[(size_t)t * D + c] = fmaf(wld(table, row + c), scale, wld(positions, prow + c));
+        return;
+    }
     for (uint32_t c = threadIdx.x; c < D; c += blockDim.x) dst[(size_t)t * D + c] = wld(table, row + c) * scale;
 }
 
@@ -292,6 +298,46 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
             st[c] = h;
             last[row + c] = fmaf(prev - h, wld(shift_mix, c), h);
         }
+    }
+}
+
+// Kinds without row statistics (Dynamic Tanh; the plain residual step) and their combinations with the others: one CTA per row,
+// nothing cached.  dst = (res +) f(src) and, with dst2, dst2 = f2(dst): the residual step that closes a sublayer and the
+// Dynamic Tanh that opens the next are one launch.
+template <typename WT>
+__device__ void norm_any_pass(float* out, const float* x, const float* res, const WT* __restrict__ w, uint32_t cols, uint32_t kind, float eps, float gain,
+                              float* sh) {
+    float mean = 0.0f, inv = 1.0f;
+    if (!(kind & 24u)) {
+        if (!(kind & 1u)) {
+            float sum = 0.0f;
+            for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) sum += x[c];
+            mean = block_sum(sum, sh) / (float)cols;
+        }
+        float q = 0.0f;
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = x[c] - mean; q = fmaf(d, d, q); }
+        inv = 1.0f / sqrtf(block_sum(q, sh) / (float)cols + eps);
+    }
+    const float g = (kind & 4u) ? gain : 1.0f;
+    const float alpha = (kind & 8u) ? wld(w, (size_t)2 * cols) : 0.0f;
+    for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+        float y;
+        if (kind & 16u) y = x[c] * g;
+        else if (kind & 8u) y = fmaf(tanhf(alpha * x[c]), wld(w, c), wld(w, (size_t)cols + c)) * g;
+        else y = (x[c] - mean) * inv * norm_weight(wld(w, c), kind, gain);
+        out[c] = res ? res[c] + y : y;
+    }
+}
+template <typename WT>
+__global__ void k_norm_any(float* dst, const float* src, const WT* __restrict__ w, const float* res, uint32_t cols, uint32_t kind, float eps,
+                           float* dst2, const WT* __restrict__ w2, uint32_t kind2, float gain) {
+    pdl_enter();
+    __shared__ float sh[32];
+    const size_t row = (size_t)blockIdx.x * cols;
+    norm_any_pass(dst + row, src + row, res ? res + row : nullptr, w, cols, kind, eps, gain, sh);
+    if (dst2) {
+        __syncthreads();                               // the row just written is read back by other threads
+        norm_any_pass(dst2 + row, dst + row, (const float*)nullptr, w2, cols, kind2, eps, gain, sh);
     }
 }
 
@@ -677,13 +723,13 @@ static void launch_window_attention_tiled(const ZgSeqOp& s, float* const* bufs, 
 template <typename WT>
 __global__ void k_causal_conv(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ w, float* state,
                               const float* __restrict__ ctl, uint32_t T, uint32_t C, uint32_t taps, uint32_t src_rs, uint32_t dst_rs, uint32_t act,
-                              uint32_t advance) {
+                              uint32_t advance, const WT* __restrict__ bias) {
     pdl_enter();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= (size_t)T * C) return;
     const uint32_t t = (uint32_t)(e / C), c = (uint32_t)(e % C);
     float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * (taps - 1) * C;
-    float y = 0.0f;
+    float y = bias ? wld(bias, c) : 0.0f;
     for (uint32_t j = 0; j < taps; j++) {
         const int tau = (int)t - (int)(taps - 1) + (int)j;     // time relative to the step's first token
         const float x = tau >= 0 ? src[(size_t)tau * src_rs + c] : st[(size_t)(tau + (int)(taps - 1)) * C + c];
@@ -952,14 +998,14 @@ __global__ void k_delta_out(float* __restrict__ dst, const float* __restrict__ g
 // ── ROUTE: one warp per token ────────────────────────────────────────────────────────────────────────────────────
 template <typename WT>
 __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logits, const WT* __restrict__ corr, uint32_t T, uint32_t NE, uint32_t top,
-                        uint32_t logits_rs, uint32_t mode) {
+                        uint32_t logits_rs, uint32_t mode, uint32_t groups, uint32_t keep) {
     pdl_enter();
-    extern __shared__ float sm[];                      // [warps][NE] choice scores
+    extern __shared__ float sm[];                      // [warps][NE + groups] choice scores, group scores
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t t = blockIdx.x * (blockDim.x >> 5) + warp;
     if (t >= T) return;
     const float* z = logits + (size_t)t * logits_rs;
-    float* ch = sm + warp * NE;
+    float* ch = sm + warp * (NE + groups);
     float mx = -INFINITY, inv = 0.0f;
     if (mode == 0) {
         for (uint32_t e = lane; e < NE; e += 32) mx = fmaxf(mx, z[e]);
@@ -968,8 +1014,38 @@ __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logit
         for (uint32_t e = lane; e < NE; e += 32) sum += expf(z[e] - mx);
         inv = 1.0f / warp_sum(sum);
         for (uint32_t e = lane; e < NE; e += 32) ch[e] = expf(z[e] - mx) * inv + wld(corr, e);
-    } else {
+    } else if (mode == 1) {
         for (uint32_t e = lane; e < NE; e += 32) ch[e] = z[e] + wld(corr, e);   // biased logits choose AND weigh
+    } else {
+        for (uint32_t e = lane; e < NE; e += 32) ch[e] = sigmoidf_(z[e]) + wld(corr, e);
+        if (groups > 1) {                              // only outputs of the `keep` best groups stay eligible
+            float* gs = ch + NE;
+            const uint32_t per = NE / groups;
+            __syncwarp();
+            for (uint32_t g = lane; g < groups; g += 32) {   // a group scores the sum of its two largest choice scores
+                float a = -INFINITY, b = -INFINITY;
+                for (uint32_t e = g * per; e < (g + 1) * per; e++) {
+                    const float v = ch[e];
+                    if (v > a) { b = a; a = v; } else if (v > b) b = v;
+                }
+                gs[g] = per > 1 ? a + b : a;
+            }
+            __syncwarp();
+            uint32_t kept_mine = 0;                    // bit i: group lane + 32 i is kept (groups <= 1024)
+            for (uint32_t c = 0; c < keep; c++) {
+                float best = -INFINITY; uint32_t bi = 0xFFFFFFFFu;
+                for (uint32_t g = lane; g < groups; g += 32) if (!((kept_mine >> (g / 32)) & 1u) && (gs[g] > best || bi == 0xFFFFFFFFu)) { best = gs[g]; bi = g; }
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (oi != 0xFFFFFFFFu && (bi == 0xFFFFFFFFu || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+                }
+                if (bi != 0xFFFFFFFFu && bi % 32 == lane) kept_mine |= 1u << (bi / 32);
+            }
+            for (uint32_t g = lane; g < groups; g += 32)
+                if (!((kept_mine >> (g / 32)) & 1u))
+                    for (uint32_t e = g * per; e < (g + 1) * per; e++) ch[e] = -INFINITY;
+        }
     }
     __syncwarp();
     float first = 0.0f, chosen_sum = 0.0f;             // mode 1 (lane 0): the largest chosen logit and the sum of exp(z - first)
@@ -985,6 +1061,7 @@ __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logit
             float* out = dst + ((size_t)t * top + c) * 2;
             reinterpret_cast<int*>(out)[0] = (int)bi;
             if (mode == 0) out[1] = bi < NE ? expf(z[bi] - mx) * inv : 0.0f;
+            else if (mode == 2) { out[1] = bi < NE ? sigmoidf_(z[bi]) : 0.0f; chosen_sum += out[1]; }
             else {
                 if (c == 0) first = best;
                 out[1] = bi < NE ? expf(best - first) : 0.0f;
@@ -994,8 +1071,8 @@ __global__ void k_route(float* __restrict__ dst, const float* __restrict__ logit
         }
         __syncwarp();
     }
-    if (mode == 1 && lane == 0) {
-        const float norm = 1.0f / chosen_sum;
+    if (mode != 0 && lane == 0) {
+        const float norm = 1.0f / (mode == 2 ? chosen_sum + 1e-20f : chosen_sum);
         for (uint32_t c = 0; c < top; c++) dst[((size_t)t * top + c) * 2 + 1] *= norm;
     }
 }
@@ -1235,6 +1312,7 @@ uint32_t zg_delta_row_slices(uint32_t dim) {
 
 // Static checks of a sequence op against the program's buffer sizes (f32 slots): shapes, strides and every extent.
 bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n) {
+    if (op.tag >= ZG_OP_SSM_SCAN) return zg_rec_op_valid(op, elems, n_bufs, why, why_n);
     if (op.tag >= ZG_OP_TOKEN_SHIFT) return zg_mix_op_valid(op, elems, n_bufs, why, why_n);
     const ZgSeqOp& s = op.u.seq;
     auto fail = [&](const char* m) { snprintf(why, why_n, "%s", m); return false; };
@@ -1260,8 +1338,10 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         }
         case ZG_OP_NORM: {
             const size_t n = (size_t)s.n[0] * s.n[1];
-            if (!n || s.n[2] > 7) return fail("norm: shape");
-            if (!fits(0, s.off[3], n) || !fits(1, 0, n) || !wfits(2, s.off[0], s.n[1])) return fail("norm: extent");
+            if (!n || s.n[2] > 31 || (s.n[2] & 24u) == 24u) return fail("norm: shape");
+            const size_t w_need = (s.n[2] & 8u) ? 2 * (size_t)s.n[1] + 1 : s.n[1];      // Dynamic Tanh: weight, bias and alpha
+            if (!fits(0, s.off[3], n) || !fits(1, 0, n) || (!(s.n[2] & 16u) && !wfits(2, s.off[0], w_need))) return fail("norm: extent");
+            if (((s.n[2] | (s.buf[4] != ZG_NO_BUF && !s.n[5] ? s.n[4] : 0u)) & 24u) && (s.n[5] || s.buf[6] != ZG_NO_BUF)) return fail("norm: kinds without statistics take no averaged source and no token shift");
             if (s.n[5]) {      // averaged source
                 if (s.n[6] < n || !fits(1, 0, (size_t)(s.n[5] - 1) * s.n[6] + n) || !wfits(2, s.off[4], s.n[5]) || s.buf[3] != ZG_NO_BUF || !fits(4, 0, n) || s.buf[4] == s.buf[0] ||
                     s.buf[4] == s.buf[1])
@@ -1270,7 +1350,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
                 return true;
             }
             if (s.buf[3] != ZG_NO_BUF && !fits(3, 0, n)) return fail("norm: residual extent");
-            if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 7 || !fits(4, 0, n) || !wfits(5, s.off[1], s.n[1]) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
+            if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 31 || (s.n[4] & 24u) == 24u || !fits(4, 0, n) || (!(s.n[4] & 16u) && !wfits(5, s.off[1], (s.n[4] & 8u) ? 2 * (size_t)s.n[1] + 1 : s.n[1])) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
                 return fail("norm: chained norm");
             if (s.buf[6] != ZG_NO_BUF && (s.n[0] != 1 || !have(6) || elems[s.buf[6]] < s.n[1] || !wfits(s.buf[4] != ZG_NO_BUF ? 5 : 2, s.off[2], s.n[1]) || !fits(7, 0, ZG_CTL_IDS)))
                 return fail("norm: fused token shift (single-row steps)");
@@ -1290,6 +1370,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!fits(0, s.off[2], (T - 1) * drs + C) || !fits(1, s.off[1], (T - 1) * srs + C) || !wfits(2, s.off[0], C * taps) || !have(3) || !fits(4, 0, ZG_CTL_IDS))
                 return fail("causal_conv: extent");
             if (taps > 1 && elems[s.buf[3]] < (taps - 1) * C) return fail("causal_conv: state size");
+            if (s.n[7] > 1 || (s.n[7] && !wfits(2, s.off[3], C))) return fail("causal_conv: bias");
             if (s.buf[0] == s.buf[1]) return fail("causal_conv: in place");
             return true;
         }
@@ -1305,7 +1386,8 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         }
         case ZG_OP_ROUTE: {
             const size_t T = s.n[0], NE = s.n[1], top = s.n[2], rs = s.n[3];
-            if (!T || !NE || !top || top > NE || rs < NE || NE > 4096 || s.n[5] > 1) return fail("route: shape");
+            if (!T || !NE || !top || top > NE || rs < NE || NE > 4096 || s.n[5] > 2) return fail("route: shape");
+            if (s.n[5] == 2 && s.n[6] > 1 && (NE % s.n[6] || s.n[6] > 1024 || !s.n[7] || s.n[7] > s.n[6] || (size_t)s.n[7] * (NE / s.n[6]) < top)) return fail("route: groups");
             if (!fits(0, 0, T * top * 2) || !fits(1, s.off[1], (T - 1) * rs + NE) || !wfits(2, s.off[0], NE)) return fail("route: extent");
             return true;
         }
@@ -1330,7 +1412,7 @@ uint32_t zg_seq_op_writes(uint32_t tag) {
         case ZG_OP_CAUSAL_CONV: return 1u | (1u << 3);
         case ZG_OP_DELTA_RULE: return 1u | (1u << 6);
         case ZG_OP_MOE_FFN: return 1u | (1u << 4);
-        default: return tag >= ZG_OP_TOKEN_SHIFT ? zg_mix_op_writes(tag) : 1u;
+        default: return tag >= ZG_OP_SSM_SCAN ? zg_rec_op_writes(tag) : (tag >= ZG_OP_TOKEN_SHIFT ? zg_mix_op_writes(tag) : 1u);
     }
 }
 
@@ -1345,6 +1427,7 @@ static uint32_t attention_splits(const ZgSeqOp& s) {
     return S < 2 ? 1 : (S > 16 ? 16 : S);
 }
 size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
+    if (op.tag >= ZG_OP_SSM_SCAN) return 0;
     if (op.tag >= ZG_OP_TOKEN_SHIFT) return zg_mix_op_scratch_elems(op);
     if (op.tag == ZG_OP_WINDOW_ATTENTION) {
         const uint32_t S = attention_splits(op.u.seq);
@@ -1365,7 +1448,8 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
     const ZgSeqOp& s = op.u.seq;
     switch (op.tag) {
         case ZG_OP_EMBED:
-            ZG_SEQ_WDT(s.n[2], launch_pdl(k_embed<WT>, dim3(s.n[0]), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), s.n[1], s.f[0]));
+            ZG_SEQ_WDT(s.n[2], launch_pdl(k_embed<WT>, dim3(s.n[0]), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), s.n[1], s.f[0],
+                                          s.n[3] ? wptr<WT>(bufs, s.buf[2], s.off[1]) : nullptr));
             ZG_SEQ_CHECK();
             return true;
         case ZG_OP_LINEAR: {
@@ -1401,6 +1485,13 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             float* dst2 = s.buf[4] != ZG_NO_BUF ? bufs[s.buf[4]] : nullptr;
             float* shift_state = s.buf[6] != ZG_NO_BUF ? bufs[s.buf[6]] : nullptr;
             const uint32_t avg_terms = s.n[5];             // averaged source: buf 4 receives the average instead of a chained norm
+            if ((s.n[2] | (dst2 ? s.n[4] : 0u)) & 24u) {   // Dynamic Tanh or the plain residual step somewhere in the launch
+                ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm_any<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]] + s.off[3], (const float*)bufs[s.buf[1]],
+                                              (s.n[2] & 16u) ? (const WT*)nullptr : wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0], dst2,
+                                              dst2 && !(s.n[4] & 16u) ? wptr<WT>(bufs, s.buf[5], s.off[1]) : (const WT*)nullptr, s.n[4], s.f[1]));
+                ZG_SEQ_CHECK();
+                return true;
+            }
             if (avg_terms) dst2 = nullptr;
             ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]] + s.off[3], bufs[s.buf[1]], wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0],
                                           dst2, dst2 ? wptr<WT>(bufs, s.buf[5], s.off[1]) : nullptr, s.n[4], s.f[1],
@@ -1459,7 +1550,8 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const float* src = bufs[s.buf[1]] + s.off[1];
             const size_t n = (size_t)T * C;
             ZG_SEQ_WDT(s.n[6], launch_pdl(k_causal_conv<WT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, dst, src, wptr<WT>(bufs, s.buf[2], s.off[0]), bufs[s.buf[3]], bufs[s.buf[4]],
-                                                                                          T, C, taps, s.n[3], s.n[4], s.n[5], (uint32_t)(T == 1 && taps > 1)));
+                                                                                          T, C, taps, s.n[3], s.n[4], s.n[5], (uint32_t)(T == 1 && taps > 1),
+                                                                                          s.n[7] ? wptr<WT>(bufs, s.buf[2], s.off[3]) : nullptr));
             ZG_SEQ_CHECK();
             if (taps > 1 && T > 1) {
                 launch_pdl(k_conv_advance, dim3((C + 127) / 128), dim3(128), 0, st, bufs[s.buf[3]], src, bufs[s.buf[4]], T, C, taps, s.n[3]);
@@ -1499,8 +1591,9 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         }
         case ZG_OP_ROUTE: {
             const uint32_t T = s.n[0], NE = s.n[1];
-            ZG_SEQ_WDT(s.n[4], launch_pdl(k_route<WT>, dim3((T + 3) / 4), dim3(128), 4 * NE * sizeof(float), st, bufs[s.buf[0]], bufs[s.buf[1]] + s.off[1], wptr<WT>(bufs, s.buf[2], s.off[0]), T, NE,
-                                                                                         s.n[2], s.n[3], s.n[5]));
+            const uint32_t groups = s.n[5] == 2 && s.n[6] > 1 ? s.n[6] : 0;
+            ZG_SEQ_WDT(s.n[4], launch_pdl(k_route<WT>, dim3((T + 3) / 4), dim3(128), 4 * (NE + groups) * sizeof(float), st, bufs[s.buf[0]], bufs[s.buf[1]] + s.off[1], wptr<WT>(bufs, s.buf[2], s.off[0]), T, NE,
+                                                                                         s.n[2], s.n[3], s.n[5], groups, s.n[7]));
             ZG_SEQ_CHECK();
             return true;
         }
@@ -1538,6 +1631,6 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             return true;
         }
         default:
-            return zg_launch_mix_op(op, bufs, scratch, st);
+            return op.tag >= ZG_OP_SSM_SCAN ? zg_launch_rec_op(op, bufs, st) : zg_launch_mix_op(op, bufs, scratch, st);
     }
 }
