@@ -61,7 +61,7 @@ class PepevikConfig:
             if kind not in MIXERS:
                 raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
             owner = L.get("weights_of", i)
-            if owner != i:
+            if "weights_of" in L:
                 if not (0 <= owner < i) or "weights_of" in c["layers"][owner]:
                     raise ValueError(f"layer {i}: weights_of must name an earlier layer with tensors of its own")
                 o = c["layers"][owner]
