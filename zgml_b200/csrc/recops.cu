@@ -11,153 +11,209 @@ namespace {
 
 // ── SSM_SCAN ─────────────────────────────────────────────────────────────────────────────────────────────────────
 // Columns of a head's state S [N, P] evolve independently given the token's B, C, decay and step size, so a head is split by
-// columns over CTAs.  A thread keeps kSsmRows state rows of one column in registers; the NS threads of a column sit in
-// adjacent lanes (NS a power of two <= 32) and meet by shuffles for the read-out.  Thread s of a column owns rows
-// 4 s + 4 NS q + i (q < 2, i < 4): the NS lanes read consecutive float4s of B and C from shared memory.  Per token the
-// critical path is one FMA per state element: S = a S + (dt x) B; the read-out sum hangs off it.
-// The per-token operands of a tile of tokens (B, C, the CTA's x columns, dt and the decay) are staged in shared memory by
-// the whole CTA; two tiles are in flight, so the next tile's loads run under this tile's walk.
-// State in memory: [H][column blocks][kSsmRows][kSsmThreads], element (i, thread) — each thread's rows, fully coalesced;
-// the layout is private to the op (zeros mean an empty state in any layout).
-constexpr int kSsmRows = 8, kSsmThreads = 128, kSsmTile = 16, kSsmMaxN = kSsmRows * 32;
+// columns over CTAs.  A thread keeps RP state rows of one column in registers; the NS threads of a column sit in adjacent
+// lanes (NS a power of two <= 32) and meet by shuffles for the read-out.  Thread s of a column owns rows 4 s + 4 NS q + i
+// (q < RP / 4, i < 4): the NS lanes read consecutive float4s of B and C from shared memory.  Per token the critical path is
+// one FMA per state element, S = a S + (dt x) B; the read-out sum hangs off it.
+// Step sizes and decays of the head (softplus, two exponentials) are evaluated for a span of tokens at once, in parallel,
+// before the walk; B, C and the CTA's x columns arrive in tiles of kSsmTile tokens through cp.async, two tiles in flight, so
+// the next tile's loads run under this tile's walk.
+// State in memory: [H][column blocks][RP][kSsmThreads], element (i, thread) — each thread's rows, fully coalesced; the layout
+// is private to the op (zeros mean an empty state in any layout).
+constexpr int kSsmThreads = 128, kSsmTile = 16, kSsmSpan = 1024, kSsmMaxN = 16 * 32;
+__host__ __device__ inline uint32_t ssm_rows(uint32_t N) { return N > 8 * 32 ? 16 : 8; }
 __host__ __device__ inline uint32_t ssm_slices(uint32_t N) {
     uint32_t ns = 1;
-    while (ns * kSsmRows < N) ns <<= 1;
+    while (ns * ssm_rows(N) < N) ns <<= 1;
     return ns;
 }
 struct SsmArgs {
     float* dst; const float* xbc; const float* dtl; float* state; const float* ctl;
-    uint32_t T, H, G, N, P, x_off, b_off, c_off, dt_off, xbc_rs, dt_rs;
+    uint32_t T, H, G, N, P, x_off, b_off, c_off, dt_off, xbc_rs, dt_rs, vec;
 };
-template <typename WT, uint32_t NS>
+// global -> shared without passing through registers, 4 or 16 bytes; `on` false writes zeros (nothing is read)
+__device__ __forceinline__ void ssm_copy4(float* dst, const float* src, bool on) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = on ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void ssm_copy16(float* dst, const float* src, bool on) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = on ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+template <typename WT, uint32_t NS, int RP>
 __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* __restrict__ a_log, const WT* __restrict__ dt_bias, const WT* __restrict__ dskip) {
     pdl_enter();
-    constexpr uint32_t CP = kSsmThreads / NS, NP = NS * kSsmRows;     // columns per CTA, padded state rows
+    constexpr uint32_t CP = kSsmThreads / NS, NP = NS * RP;     // columns per CTA, padded state rows
+    constexpr uint32_t XP = (CP + 3) & ~3u;                      // x columns of a tile row, padded to 16 bytes
     extern __shared__ __align__(16) float sm[];
-    // per stage: B [tile][NP], C [tile][NP], x [tile][CP], dt [tile], decay [tile]
-    constexpr uint32_t kStage = kSsmTile * (2 * NP + CP + 2);
+    constexpr uint32_t kStage = kSsmTile * (2 * NP + XP);       // per stage: B [tile][NP], C [tile][NP], x [tile][XP]
+    float* Dt = sm + 2 * kStage;                                // step sizes and decays of a span of tokens
+    float* Dec = Dt + kSsmSpan;
     const uint32_t tid = threadIdx.x, s = tid % NS, pl = tid / NS;
     const uint32_t h = blockIdx.y, cb = blockIdx.x, g = h / (a.H / a.G);
     const uint32_t p = cb * CP + pl;
     const bool col_ok = p < a.P;
     const uint32_t slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
     const uint32_t n_cb = (a.P + CP - 1) / CP;
-    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (kSsmRows * kSsmThreads);
-    float S[kSsmRows];
+    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (RP * kSsmThreads);
+    float S[RP];
 #pragma unroll
-    for (int i = 0; i < kSsmRows; i++) S[i] = st[i * kSsmThreads + tid];
+    for (int i = 0; i < RP; i++) S[i] = st[i * kSsmThreads + tid];
     const float neg_a = -expf(wld(a_log, h)), bias = wld(dt_bias, h), dsk = wld(dskip, h);
+    const float* bsrc = a.xbc + a.b_off + (size_t)g * a.N;
+    const float* csrc = a.xbc + a.c_off + (size_t)g * a.N;
+    const float* xsrc = a.xbc + a.x_off + (size_t)h * a.P + (size_t)cb * CP;
+    const uint32_t x_cols = min(CP, a.P - cb * CP);
 
-    auto stage_tile = [&](uint32_t t0, uint32_t stage) {
+    auto fetch_tile = [&](uint32_t t0, uint32_t stage) {
         float* Bs = sm + stage * kStage;
         float* Cs = Bs + kSsmTile * NP;
         float* Xs = Cs + kSsmTile * NP;
-        float* Ds = Xs + kSsmTile * CP;
-        float* As = Ds + kSsmTile;
         const uint32_t nt = min((uint32_t)kSsmTile, a.T - t0);
-        for (uint32_t e = tid; e < nt * NP; e += kSsmThreads) {
-            const uint32_t tt = e / NP, n = e % NP;
-            const float* row = a.xbc + (size_t)(t0 + tt) * a.xbc_rs + (size_t)g * a.N;
-            Bs[e] = n < a.N ? row[a.b_off + n] : 0.0f;
-            Cs[e] = n < a.N ? row[a.c_off + n] : 0.0f;
+        if (a.vec) {
+            for (uint32_t e = tid; e < nt * (NP / 4); e += kSsmThreads) {
+                const uint32_t tt = e / (NP / 4), n = 4 * (e % (NP / 4));
+                const bool on = n < a.N;
+                ssm_copy16(Bs + tt * NP + n, on ? bsrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
+                ssm_copy16(Cs + tt * NP + n, on ? csrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
+            }
+            if (CP >= 4) {
+                for (uint32_t e = tid; e < nt * (XP / 4); e += kSsmThreads) {
+                    const uint32_t tt = e / (XP / 4), c = 4 * (e % (XP / 4));
+                    const bool on = c < x_cols;
+                    ssm_copy16(Xs + tt * XP + c, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
+                }
+                return;
+            }
+        } else {
+            for (uint32_t e = tid; e < nt * NP; e += kSsmThreads) {
+                const uint32_t tt = e / NP, n = e % NP;
+                const bool on = n < a.N;
+                ssm_copy4(Bs + e, on ? bsrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
+                ssm_copy4(Cs + e, on ? csrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
+            }
         }
         for (uint32_t e = tid; e < nt * CP; e += kSsmThreads) {
-            const uint32_t tt = e / CP, c = cb * CP + e % CP;
-            Xs[e] = c < a.P ? a.xbc[(size_t)(t0 + tt) * a.xbc_rs + a.x_off + (size_t)h * a.P + c] : 0.0f;
-        }
-        if (tid < nt) {
-            const float dt = softplusf_(a.dtl[(size_t)(t0 + tid) * a.dt_rs + a.dt_off + h] + bias);
-            Ds[tid] = dt;
-            As[tid] = expf(neg_a * dt);
+            const uint32_t tt = e / CP, c = e % CP;
+            const bool on = c < x_cols;
+            ssm_copy4(Xs + tt * XP + c, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
         }
     };
-    for (uint32_t t0 = 0, it = 0; t0 < a.T; t0 += kSsmTile, it++) {
-        const uint32_t stage = it & 1;
-        stage_tile(t0, stage);                          // the other stage may still be read by slower warps: two stages, one barrier
-        __syncthreads();
-        const float* Bs = sm + stage * kStage;
-        const float* Cs = Bs + kSsmTile * NP;
-        const float* Xs = Cs + kSsmTile * NP;
-        const float* Ds = Xs + kSsmTile * CP;
-        const float* As = Ds + kSsmTile;
-        const uint32_t nt = min((uint32_t)kSsmTile, a.T - t0);
-        for (uint32_t tt = 0; tt < nt; tt++) {
-            const float x = Xs[tt * CP + pl], dec = As[tt], dtx = Ds[tt] * x;
-            float y = 0.0f;
+    for (uint32_t base = 0; base < a.T; base += kSsmSpan) {
+        const uint32_t span = min((uint32_t)kSsmSpan, a.T - base);
+        __syncthreads();                                   // the previous span's readers are done
+        fetch_tile(base, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        for (uint32_t t = tid; t < span; t += kSsmThreads) {
+            const float dt = softplusf_(a.dtl[(size_t)(base + t) * a.dt_rs + a.dt_off + h] + bias);
+            Dt[t] = dt;
+            Dec[t] = expf(neg_a * dt);
+        }
+        for (uint32_t t0 = 0, it = 0; t0 < span; t0 += kSsmTile, it++) {
+            const uint32_t stage = it & 1;
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();                               // tile `it` has landed for everyone, and everyone has left tile it - 1
+            if (t0 + kSsmTile < span) fetch_tile(base + t0 + kSsmTile, stage ^ 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            const float* Bs = sm + stage * kStage;
+            const float* Cs = Bs + kSsmTile * NP;
+            const float* Xs = Cs + kSsmTile * NP;
+            const uint32_t nt = min((uint32_t)kSsmTile, span - t0);
+            for (uint32_t tt = 0; tt < nt; tt++) {
+                const float x = Xs[tt * XP + pl], dec = Dec[t0 + tt], dtx = Dt[t0 + tt] * x;
+                float y = 0.0f;
 #pragma unroll
-            for (int q = 0; q < kSsmRows / 4; q++) {
-                const float4 b = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * (s + NS * q));
-                const float4 c = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * (s + NS * q));
-                S[4 * q + 0] = fmaf(dec, S[4 * q + 0], dtx * b.x);
-                S[4 * q + 1] = fmaf(dec, S[4 * q + 1], dtx * b.y);
-                S[4 * q + 2] = fmaf(dec, S[4 * q + 2], dtx * b.z);
-                S[4 * q + 3] = fmaf(dec, S[4 * q + 3], dtx * b.w);
-                y = fmaf(S[4 * q + 0], c.x, fmaf(S[4 * q + 1], c.y, fmaf(S[4 * q + 2], c.z, fmaf(S[4 * q + 3], c.w, y))));
+                for (int q = 0; q < RP / 4; q++) {
+                    const float4 b = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * (s + NS * q));
+                    const float4 c = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * (s + NS * q));
+                    S[4 * q + 0] = fmaf(dec, S[4 * q + 0], dtx * b.x);
+                    S[4 * q + 1] = fmaf(dec, S[4 * q + 1], dtx * b.y);
+                    S[4 * q + 2] = fmaf(dec, S[4 * q + 2], dtx * b.z);
+                    S[4 * q + 3] = fmaf(dec, S[4 * q + 3], dtx * b.w);
+                    y = fmaf(S[4 * q + 0], c.x, fmaf(S[4 * q + 1], c.y, fmaf(S[4 * q + 2], c.z, fmaf(S[4 * q + 3], c.w, y))));
+                }
+#pragma unroll
+                for (uint32_t o = NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+                if (s == 0 && col_ok) a.dst[(size_t)(base + t0 + tt) * a.H * a.P + (size_t)h * a.P + p] = fmaf(dsk, x, y);
             }
-#pragma unroll
-            for (uint32_t o = NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (s == 0 && col_ok) a.dst[(size_t)(t0 + tt) * a.H * a.P + (size_t)h * a.P + p] = fmaf(dsk, x, y);
         }
     }
 #pragma unroll
-    for (int i = 0; i < kSsmRows; i++) st[i * kSsmThreads + tid] = S[i];
+    for (int i = 0; i < RP; i++) st[i * kSsmThreads + tid] = S[i];
 }
 static size_t ssm_state_elems(uint32_t H, uint32_t N, uint32_t P) {
     const uint32_t CP = kSsmThreads / ssm_slices(N);
-    return (size_t)H * ((P + CP - 1) / CP) * kSsmRows * kSsmThreads;
+    return (size_t)H * ((P + CP - 1) / CP) * ssm_rows(N) * kSsmThreads;
 }
 
-// ── MIN_GRU: one thread per channel, the tokens walked in order ──────────────────────────────────────────────────
-// The gate and the candidate of a token do not depend on the state, so four tokens' worth are evaluated ahead of the chain
-// S <- S + z (c - S), which is all that is serial.
-__global__ void k_min_gru(float* __restrict__ dst, const float* __restrict__ proj, float* __restrict__ state, const float* __restrict__ ctl,
-                          uint32_t T, uint32_t W, uint32_t rs, uint32_t drs, uint32_t z_off, uint32_t u_off, uint32_t g_off) {
+// ── MIN_GRU ──────────────────────────────────────────────────────────────────────────────────────────────────────
+// S_t = (1 - z_t) S_{t-1} + z_t c_t is a linear recurrence per channel whose coefficients do not depend on the state, so the
+// step's tokens are cut into up to 32 segments that are walked side by side: thread (channel, segment) first walks its segment
+// from an empty state, keeping the product of the (1 - z) and the value reached; the segments' (product, value) pairs are then
+// folded in order, which gives every segment the state it starts from; the second walk writes the outputs.  A single-token
+// step is one segment of one token.
+constexpr int kGruChannels = 32, kGruMaxSegments = 32;
+__device__ __forceinline__ void gru_terms(const float* row, uint32_t z_off, uint32_t u_off, uint32_t c, float& z, float& cand) {
+    const float u = row[u_off + c];
+    z = sigmoidf_(row[z_off + c]);
+    cand = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
+}
+__global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_min_gru(float* __restrict__ dst, const float* __restrict__ proj, float* __restrict__ state,
+                                                                            const float* __restrict__ ctl, uint32_t T, uint32_t W, uint32_t rs, uint32_t drs,
+                                                                            uint32_t z_off, uint32_t u_off, uint32_t g_off, uint32_t seg_len) {
     pdl_enter();
-    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= W) return;
+    __shared__ float segA[kGruMaxSegments][kGruChannels], segB[kGruMaxSegments][kGruChannels];
+    const uint32_t c = blockIdx.x * kGruChannels + threadIdx.x, seg = threadIdx.y, n_seg = blockDim.y;
+    const bool on = c < W;
+    const uint32_t t_begin = min(T, seg * seg_len), t_end = min(T, t_begin + seg_len);
     float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * W;
-    float S = st[c];
-    for (uint32_t t0 = 0; t0 < T; t0 += 4) {
-        float z[4], cand[4], gate[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (t0 + i < T) {
-                const float* row = proj + (size_t)(t0 + i) * rs;
-                const float u = row[u_off + c], gl = row[g_off + c];
-                z[i] = sigmoidf_(row[z_off + c]);
-                cand[i] = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
-                gate[i] = gl * sigmoidf_(gl);
+    float S = 0.0f;
+    if (n_seg > 1) {
+        float A = 1.0f;
+        if (on)
+            for (uint32_t t = t_begin; t < t_end; t++) {
+                float z, cand;
+                gru_terms(proj + (size_t)t * rs, z_off, u_off, c, z, cand);
+                A *= 1.0f - z;
+                S = fmaf(z, cand, (1.0f - z) * S);
             }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (t0 + i < T) {
-                S = fmaf(z[i], cand[i], (1.0f - z[i]) * S);
-                dst[(size_t)(t0 + i) * drs + c] = S * gate[i];
-            }
-        }
+        segA[seg][threadIdx.x] = A;
+        segB[seg][threadIdx.x] = S;
+        __syncthreads();
     }
-    st[c] = S;
+    if (!on) return;
+    S = st[c];
+    for (uint32_t j = 0; j < seg; j++) S = fmaf(segA[j][threadIdx.x], S, segB[j][threadIdx.x]);
+    for (uint32_t t = t_begin; t < t_end; t++) {
+        const float* row = proj + (size_t)t * rs;
+        float z, cand;
+        gru_terms(row, z_off, u_off, c, z, cand);
+        const float gl = row[g_off + c];
+        S = fmaf(z, cand, (1.0f - z) * S);
+        dst[(size_t)t * drs + c] = S * (gl * sigmoidf_(gl));
+    }
+    if (seg == n_seg - 1) st[c] = S;
 }
 
-// ── GATED_NORM: one warp per (token, group) ──────────────────────────────────────────────────────────────────────
+// ── GATED_NORM: one CTA per (token, group) ───────────────────────────────────────────────────────────────────────
 template <typename WT>
-__global__ void k_gated_norm(float* dst, const float* src, const float* __restrict__ gate, const WT* __restrict__ w, uint32_t T, uint32_t cols,
-                             uint32_t groups, uint32_t gate_rs, uint32_t src_rs, uint32_t dst_rs, float eps) {
+__global__ void k_gated_norm(float* dst, const float* src, const float* __restrict__ gate, const WT* __restrict__ w, uint32_t cols, uint32_t groups,
+                             uint32_t gate_rs, uint32_t src_rs, uint32_t dst_rs, float eps) {
     pdl_enter();
-    const uint32_t item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (item >= T * groups) return;
-    const uint32_t t = item / groups, gi = item % groups, gs = cols / groups, c0 = gi * gs;
+    __shared__ float sh[32];
+    const uint32_t t = blockIdx.x / groups, gi = blockIdx.x % groups, gs = cols / groups, c0 = gi * gs;
     const float* x = src + (size_t)t * src_rs + c0;
     const float* gt = gate + (size_t)t * gate_rs + c0;
     float q = 0.0f;
-    for (uint32_t c = lane; c < gs; c += 32) {
+    for (uint32_t c = threadIdx.x; c < gs; c += blockDim.x) {
         const float z = gt[c], v = x[c] * (z * sigmoidf_(z));
         q = fmaf(v, v, q);
     }
-    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)gs + eps);
+    const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)gs + eps);
     float* out = dst + (size_t)t * dst_rs + c0;
-    for (uint32_t c = lane; c < gs; c += 32) {
+    for (uint32_t c = threadIdx.x; c < gs; c += blockDim.x) {
         const float z = gt[c], v = x[c] * (z * sigmoidf_(z));
         out[c] = v * inv * wld(w, c0 + c);
     }
@@ -270,31 +326,47 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
             a.dst = bufs[s.buf[0]]; a.xbc = bufs[s.buf[1]]; a.dtl = bufs[s.buf[2]]; a.state = bufs[s.buf[4]]; a.ctl = bufs[s.buf[5]];
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.N = s.n[3]; a.P = s.n[4]; a.x_off = s.off[0]; a.b_off = s.off[1]; a.c_off = s.off[2]; a.dt_off = s.off[3];
             a.xbc_rs = s.n[5]; a.dt_rs = s.n[6];
-            const uint32_t NS = ssm_slices(a.N), CP = kSsmThreads / NS;
+            const uint32_t NS = ssm_slices(a.N), RP = ssm_rows(a.N), CP = kSsmThreads / NS, XP = (CP + 3) & ~3u;
+            // 16-byte copies when every row of B, C and the CTA's x columns starts on a 16-byte boundary
+            a.vec = (a.N % 4 == 0 && a.P % 4 == 0 && a.xbc_rs % 4 == 0 && a.x_off % 4 == 0 && a.b_off % 4 == 0 && a.c_off % 4 == 0 &&
+                     (reinterpret_cast<uintptr_t>(a.xbc) & 15) == 0) ? 1u : 0u;
             const dim3 grid((a.P + CP - 1) / CP, a.H);
-            const size_t smem = (size_t)2 * kSsmTile * (2 * NS * kSsmRows + CP + 2) * sizeof(float);
-#define ZG_SSM(NS_)                                                                                                                       \
-    case NS_:                                                                                                                             \
-        ZG_SEQ_WDT(s.n[7], {                                                                                                              \
-            if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-            launch_pdl(k_ssm_scan<WT, NS_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
-                       wptr<WT>(bufs, s.buf[3], s.off[6]));                                                                               \
-        });                                                                                                                               \
-        break;
-            switch (NS) { ZG_SSM(1) ZG_SSM(2) ZG_SSM(4) ZG_SSM(8) ZG_SSM(16) default: ZG_SSM(32) }
+            const size_t smem = ((size_t)2 * kSsmTile * (2 * NS * RP + XP) + 2 * kSsmSpan) * sizeof(float);
+#define ZG_SSM(NS_, RP_)                                                                                                                  \
+    ZG_SEQ_WDT(s.n[7], {                                                                                                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_, RP_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        launch_pdl(k_ssm_scan<WT, NS_, RP_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
+                   wptr<WT>(bufs, s.buf[3], s.off[6]));                                                                                   \
+    })
+            if (RP == 16) ZG_SSM(32, 16);
+            else switch (NS) {
+                case 1: ZG_SSM(1, 8); break;
+                case 2: ZG_SSM(2, 8); break;
+                case 4: ZG_SSM(4, 8); break;
+                case 8: ZG_SSM(8, 8); break;
+                case 16: ZG_SSM(16, 8); break;
+                default: ZG_SSM(32, 8); break;
+            }
 #undef ZG_SSM
             ZG_SEQ_CHECK();
             return true;
         }
-        case ZG_OP_MIN_GRU:
-            launch_pdl(k_min_gru, dim3((s.n[1] + 63) / 64), dim3(64), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], s.n[0], s.n[1], s.n[2], s.n[3],
-                       s.off[0], s.off[1], s.off[2]);
+        case ZG_OP_MIN_GRU: {
+            const uint32_t T = s.n[0];
+            uint32_t n_seg = (T + 3) / 4;
+            if (n_seg > (uint32_t)kGruMaxSegments) n_seg = kGruMaxSegments;
+            const uint32_t seg_len = (T + n_seg - 1) / n_seg;
+            n_seg = (T + seg_len - 1) / seg_len;            // no empty segment at the end: the last one leaves the state behind
+            launch_pdl(k_min_gru, dim3((s.n[1] + kGruChannels - 1) / kGruChannels), dim3(kGruChannels, n_seg), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]],
+                       T, s.n[1], s.n[2], s.n[3], s.off[0], s.off[1], s.off[2], seg_len);
             ZG_SEQ_CHECK();
             return true;
+        }
         case ZG_OP_GATED_NORM: {
-            const uint32_t items = s.n[0] * s.n[2];
-            ZG_SEQ_WDT(s.n[4], launch_pdl(k_gated_norm<WT>, dim3((items + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]] + s.off[0], wptr<WT>(bufs, s.buf[3], s.off[1]),
-                                          s.n[0], s.n[1], s.n[2], s.n[3], s.n[5], s.n[6], s.f[0]));
+            const uint32_t gs = s.n[1] / s.n[2];
+            const uint32_t threads = gs <= 64 ? 32 : (gs <= 512 ? 128 : 256);
+            ZG_SEQ_WDT(s.n[4], launch_pdl(k_gated_norm<WT>, dim3(s.n[0] * s.n[2]), dim3(threads), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]] + s.off[0],
+                                          wptr<WT>(bufs, s.buf[3], s.off[1]), s.n[1], s.n[2], s.n[3], s.n[5], s.n[6], s.f[0]));
             ZG_SEQ_CHECK();
             return true;
         }
