@@ -109,6 +109,8 @@ typedef enum ZgOpTag {
  *                   (cols values) and the scalar alpha follow w in its arena; kind bit 4: no norm and no weight, the row
  *                   itself (times the gain with bit 2): dst = res + gain * src, the plain residual step of a pre-norm stack.
  *                   Bits 3 and 4 combine with a residual and a chained norm, not with the averaged source or the token shift.
+ *                   with n7 = 1 (kinds with statistics, no averaged source): buf 6 is a SECOND source, normed like the first with a
+ *                   weight of its own (off 2 of w's arena) and added to it: dst = res + norm(src) w + norm(src2) w_b
  *                   with buf 4: also dst2 = norm(dst) * w2 in the same launch (the norm closing a sublayer and the one opening the next)
  *                   with buf 6 (single-row steps): the last output of the launch then passes a TOKEN_SHIFT (mix at off 2 of the
  *                   arena of the norm it follows, state buf 6, ctl buf 7) in the same launch
@@ -116,7 +118,7 @@ typedef enum ZgOpTag {
  *                   with n 5 > 0 (no res, no chained norm): the row that is normed is the DEPTH_MIX of n5 streams of src (stride n6,
  *                   coefficients at off 4 of w's arena); buf 4 receives that average itself
  *                   buf 0 dst 1 src 2 w 3 res 4 dst2 5 w2 6 shift state 7 ctl | off 0 w 1 w2 2 shift mix 3 dst 4 average coefficients
- *                   n 0 rows 1 cols 2 kind 3 wdt 5 averaged streams 6 their stride
+ *                   n 0 rows 1 cols 2 kind 3 wdt 5 averaged streams 6 their stride 7 second source
  *                   4 kind of dst2 | f 0 eps 1 gain
  * WINDOW_ATTENTION  causal attention over the last `window` positions whose keys double as values (one projection, one cache),
  *                   grouped query heads, scores capped smoothly (cap * tanh(s / cap), f1 = 0: off), a per-distance per-head

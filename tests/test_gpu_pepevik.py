@@ -55,12 +55,14 @@ MIXED = config([ssm_layer(mlp=dense()), pair_layer(mlp=moe()), pair_layer(weight
     ssm_layer(heads=2, vdim=33, state=5, groups=2, conv=1, norm_groups=6),       # one tap: no carried inputs; more norm parts than heads
     ssm_layer(heads=1, vdim=4, state=200, groups=1, conv=6, norm_groups=2),      # a state of many rows: every lane of a column holds some
     ssm_layer(heads=4, vdim=64, state=64, groups=1, conv=2, norm_groups=4),
+    ssm_layer(heads=2, vdim=6, state=300, groups=2, conv=2, norm_groups=1),
+    ssm_layer(heads=2, vdim=20, state=2, groups=1, conv=3, norm_groups=1),       # fewer state rows than a thread holds
     pair_layer(),
     pair_layer(heads=6, kv_heads=2, dim=5, vdim=9, gru=7, every=1),              # three heads per key head; the temperature steps at every position
     pair_layer(heads=1, kv_heads=1, dim=40, vdim=3, gru=64, coef=0.0),
     pair_layer(heads=2, kv_heads=2, dim=16, vdim=16, gru=40, every=1000),        # no step of the temperature inside the prompt
     pair_layer(heads=4, kv_heads=1, dim=68, vdim=132, gru=130, every=7),
-], ids=["ssm", "ssm-3groups", "ssm-1tap", "ssm-state200", "ssm-64x64", "pair", "pair-grouped", "pair-1head", "pair-flat-temp", "pair-wide"])
+], ids=["ssm", "ssm-3groups", "ssm-1tap", "ssm-state200", "ssm-64x64", "ssm-state300", "ssm-state2", "pair", "pair-grouped", "pair-1head", "pair-flat-temp", "pair-wide"])
 def test_mixer_alone(cuda_backend, layer, dtype):
     cfg = config([layer], width=40, vocab=61)
     W = random_weights(cfg, seed=5, qk_gain=4.0)

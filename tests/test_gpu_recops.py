@@ -157,7 +157,7 @@ def test_norm_kinds_without_statistics(cuda_backend):
     Tanh; rows wider than a CTA."""
     from zgml_b200 import DeviceOp, ExternBuffer, abi
     r = np.random.default_rng(9)
-    for T, D in ((3, 40), (2, 1500)):
+    for T, D in ((3, 40), (2, 1500), (2, 4500)):
         x, res = r.standard_normal((T, D)).astype(np.float32) * 2, r.standard_normal((T, D)).astype(np.float32)
         w1, b1, a1 = (1 + 0.2 * r.standard_normal(D)).astype(np.float32), (0.1 * r.standard_normal(D)).astype(np.float32), np.float32(0.7)
         w2 = (1 + 0.2 * r.standard_normal(D)).astype(np.float32)
@@ -178,7 +178,18 @@ def test_norm_kinds_without_statistics(cuda_backend):
         got = run(cuda_backend, ops, sizes, [(1, x)], 4, x.shape, ext)
         ln = (xd - xd.mean(-1, keepdims=True)) / np.sqrt(xd.var(-1, keepdims=True) + 1e-5) * w2
         assert np.abs(got - (np.tanh(0.7 * ln) * w1 + b1)).max() < 5e-6
+        wb2 = (1 + 0.2 * r.standard_normal(D)).astype(np.float32)
+        w3, (p1, p2, p3) = weights(cuda_backend, w2, wb2, np.concatenate([w1, b1, [a1]]))
+        sizes = [x.size, x.size, w3.elems, x.size, x.size, x.size]
+        ops = [DeviceOp.norm(0, 1, 2, p1, T, D, 1e-5, abi.W_F32, kind="rms", res=3, gain=0.35, src2=5, src2_w_off=p2, then=4, then_w=2, then_w_off=p3, then_kind="dyt")]
+        both = rd + 0.35 * (rms(xd, w2) + rms(rd * 2 - 1, wb2))               # two sources, each with its own root mean square and weight
+        got = run(cuda_backend, ops, sizes, [(1, x), (3, res), (5, res * 2 - 1)], 4, x.shape, [ExternBuffer(2, w3)])
+        assert np.abs(got - (np.tanh(0.7 * both) * w1 + b1)).max() < 5e-6
+        ops = [DeviceOp.norm(0, 1, 2, p1, T, D, 1e-5, abi.W_F32, kind="rms", res=3, gain=0.35, src2=5, src2_w_off=p2)]
+        got = run(cuda_backend, ops, sizes, [(1, x), (3, res), (5, res * 2 - 1)], 0, x.shape, [ExternBuffer(2, w3)])
+        assert np.abs(got - both).max() < 5e-6
         w.free()
+        w3.free()
 
 
 def test_conv_bias_and_embed_positions(cuda_backend):

@@ -88,11 +88,12 @@ def test_state_and_lowering_shape(fake_device):
         assert all(op.u.seq.off[5] == abi.WEIGHTS_SIGMOID and op.u.seq.buf[5] != abi.NO_BUF and op.u.seq.off[6] == 100 for op in att)
         assert att[0].u.seq.buf[5] == att[1].u.seq.buf[5] != att[2].u.seq.buf[5]      # one distance table per set of weights
         assert att[0].u.seq.buf[2] != att[1].u.seq.buf[2]                               # but a cache per layer
-        # every residual step rides in the Dynamic Tanh that opens the next sublayer; the pair's first half is a step of its own
+        # every residual step rides in the Dynamic Tanh that opens the next sublayer, the pair's sum of two normed results too
         norms = [op for op in ops if op.tag == abi.OP_NORM]
         chained = [op for op in norms if op.u.seq.buf[4] != abi.NO_BUF]
         assert all(op.u.seq.n[4] == abi.NORM_DYNAMIC_TANH for op in chained)
-        assert len(norms) == 1 + 3 + (9 if head != "none" else 8) and len(chained) == (9 if head != "none" else 8)
+        assert len(norms) == 1 + (9 if head != "none" else 8) and len(chained) == len(norms) - 1
+        assert sum(op.u.seq.n[7] for op in norms) == (3 if head != "none" else 2)
         ext = [e.buf_idx for e in lp.program.externs]
         assert len(set(ext)) == len(ext) == 4 + 10 + 2                                 # weight arenas + state buffers + distance tables, each once
 

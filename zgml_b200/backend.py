@@ -218,7 +218,7 @@ class DeviceOp:
 
     @staticmethod
     def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer",
-             gain=None, shift_state=None, shift_off=0, ctl=None, dst_off=0, average=None):
+             gain=None, shift_state=None, shift_off=0, ctl=None, dst_off=0, average=None, src2=None, src2_w_off=0):
         """dst = (res +) norm(src; w); with `then`, also then = norm(dst; weights at then_w_off of arena then_w) in the same launch.
         Kinds: "layer", "rms", and "rms1" (RMS norm whose weight is stored around zero, applied as 1 + w).  `gain` multiplies the
         result(s); `shift_state` (single-row steps, with `then`) passes `then` through a token shift whose mix lies at shift_off of
@@ -226,6 +226,13 @@ class DeviceOp:
         row that is normed is sum_j coeff[j] * src[j * stride + .] (coefficients in w's arena), which also goes to buffer `out`."""
         kinds = {"layer": abi.NORM_LAYER, "rms": abi.NORM_RMS, "rms1": abi.NORM_RMS | abi.NORM_UNIT_OFFSET,
                  "dyt": abi.NORM_DYNAMIC_TANH, "none": abi.NORM_NONE}
+        if src2 is not None:
+            # Two sources, each normed with a weight of its own (both in arena w) and added: dst = res + gain (norm(src) w + norm(src2) w2).
+            assert kind in ("layer", "rms", "rms1") and average is None and shift_state is None
+            g1 = abi.NORM_GAIN if gain is not None else 0
+            return DeviceOp._seq(abi.OP_NORM, [dst, src, w, res, then, then_w if then is not None and then_kind != "none" else None, src2],
+                                 [w_off, then_w_off, src2_w_off, dst_off], [rows, cols, kinds[kind] | g1, wdt, kinds[then_kind] if then is not None else 0, 0, 0, 1],
+                                 [eps, gain if gain is not None else 0.0])
         if kind in ("dyt", "none") or (then is not None and then_kind in ("dyt", "none")):
             # Kinds without row statistics: "dyt" = tanh(alpha x) w + b (bias and alpha follow w in its arena), "none" = the row itself.
             # The gain belongs to the FIRST norm here (dst = res + gain * f(src), the residual step of a pre-norm stack).

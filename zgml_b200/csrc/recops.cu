@@ -11,20 +11,23 @@ namespace {
 
 // ── SSM_SCAN ─────────────────────────────────────────────────────────────────────────────────────────────────────
 // Columns of a head's state S [N, P] evolve independently given the token's B, C, decay and step size, so a head is split by
-// columns over CTAs.  A thread keeps RP state rows of one column in registers; the NS threads of a column sit in adjacent
-// lanes (NS a power of two <= 32) and meet by shuffles for the read-out.  Thread s of a column owns rows 4 s + 4 NS q + i
-// (q < RP / 4, i < 4): the NS lanes read consecutive float4s of B and C from shared memory.  Per token the critical path is
-// one FMA per state element, S = a S + (dt x) B; the read-out sum hangs off it.
+// columns over CTAs.  A thread keeps a block of 4 RQ state rows x 4 columns in registers: every B and C value it reads from
+// shared memory serves four columns and every x value four rows (one column per thread was bound by shared-memory
+// wavefronts, not by arithmetic).  The NS threads that share four columns sit in adjacent lanes (NS a power of two <= 32);
+// thread s owns rows 4 s + 4 NS q + i (q < RQ, i < 4), so the NS lanes read consecutive float4s of B and C.  Per token the
+// critical path is one FMA per state element, S = a S + (dt x) B.  The read-out sums of the four columns are reduced across
+// the NS lanes in a scatter: each step halves the columns a lane still carries, so four columns cost 6 shuffles, not 20.
 // Step sizes and decays of the head (softplus, two exponentials) are evaluated for a span of tokens at once, in parallel,
 // before the walk; B, C and the CTA's x columns arrive in tiles of kSsmTile tokens through cp.async, two tiles in flight, so
-// the next tile's loads run under this tile's walk.
-// State in memory: [H][column blocks][RP][kSsmThreads], element (i, thread) — each thread's rows, fully coalesced; the layout
-// is private to the op (zeros mean an empty state in any layout).
-constexpr int kSsmThreads = 128, kSsmTile = 16, kSsmSpan = 1024, kSsmMaxN = 16 * 32;
-__host__ __device__ inline uint32_t ssm_rows(uint32_t N) { return N > 8 * 32 ? 16 : 8; }
+// the next tile's loads run under this tile's walk; four tokens are walked per trip so that their loads, products and
+// reductions interleave.
+// State in memory: [H][column blocks][16 RQ][kSsmThreads], element (i, thread) — each thread's block, fully coalesced; the
+// layout is private to the op (zeros mean an empty state in any layout).
+constexpr int kSsmThreads = 128, kSsmTile = 16, kSsmSpan = 1024, kSsmMaxN = 512;
+__host__ __device__ inline uint32_t ssm_rq(uint32_t N) { return N > 256 ? 4 : (N > 128 ? 2 : 1); }
 __host__ __device__ inline uint32_t ssm_slices(uint32_t N) {
     uint32_t ns = 1;
-    while (ns * ssm_rows(N) < N) ns <<= 1;
+    while (ns * 4 * ssm_rq(N) < N) ns <<= 1;
     return ns;
 }
 struct SsmArgs {
@@ -42,30 +45,34 @@ __device__ __forceinline__ void ssm_copy16(float* dst, const float* src, bool on
     const int n = on ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
-template <typename WT, uint32_t NS, int RP>
+template <typename WT, uint32_t NS, int RQ>
 __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* __restrict__ a_log, const WT* __restrict__ dt_bias, const WT* __restrict__ dskip) {
     pdl_enter();
-    constexpr uint32_t CP = kSsmThreads / NS, NP = NS * RP;     // columns per CTA, padded state rows
-    constexpr uint32_t XP = (CP + 3) & ~3u;                      // x columns of a tile row, padded to 16 bytes
+    constexpr uint32_t CPB = kSsmThreads / NS * 4, NP = NS * 4 * RQ;     // columns per CTA, padded state rows
     extern __shared__ __align__(16) float sm[];
-    constexpr uint32_t kStage = kSsmTile * (2 * NP + XP);       // per stage: B [tile][NP], C [tile][NP], x [tile][XP]
-    float* Dt = sm + 2 * kStage;                                // step sizes and decays of a span of tokens
+    constexpr uint32_t kStage = kSsmTile * (2 * NP + CPB);               // per stage: B [tile][NP], C [tile][NP], x [tile][CPB]
+    float* Dt = sm + 2 * kStage;                                         // step sizes and decays of a span of tokens
     float* Dec = Dt + kSsmSpan;
     const uint32_t tid = threadIdx.x, s = tid % NS, pl = tid / NS;
     const uint32_t h = blockIdx.y, cb = blockIdx.x, g = h / (a.H / a.G);
-    const uint32_t p = cb * CP + pl;
-    const bool col_ok = p < a.P;
+    const uint32_t p0 = cb * CPB + pl * 4;                               // this thread's first column
     const uint32_t slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
-    const uint32_t n_cb = (a.P + CP - 1) / CP;
-    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (RP * kSsmThreads);
-    float S[RP];
+    const uint32_t n_cb = (a.P + CPB - 1) / CPB;
+    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (16 * RQ * kSsmThreads);
+    float2 S[RQ][4][2];                                                  // [q][row][column pair]: two columns per register pair, for the packed f32x2 FMA
 #pragma unroll
-    for (int i = 0; i < RP; i++) S[i] = st[i * kSsmThreads + tid];
+    for (int i = 0; i < 8 * RQ; i++) {
+        S[i / 8][(i / 2) % 4][i % 2].x = st[(2 * i) * kSsmThreads + tid];
+        S[i / 8][(i / 2) % 4][i % 2].y = st[(2 * i + 1) * kSsmThreads + tid];
+    }
     const float neg_a = -expf(wld(a_log, h)), bias = wld(dt_bias, h), dsk = wld(dskip, h);
     const float* bsrc = a.xbc + a.b_off + (size_t)g * a.N;
     const float* csrc = a.xbc + a.c_off + (size_t)g * a.N;
-    const float* xsrc = a.xbc + a.x_off + (size_t)h * a.P + (size_t)cb * CP;
-    const uint32_t x_cols = min(CP, a.P - cb * CP);
+    const float* xsrc = a.xbc + a.x_off + (size_t)h * a.P + (size_t)cb * CPB;
+    const uint32_t x_cols = min(CPB, a.P - cb * CPB);
+    // which of its four columns the thread ends up with after the scattered reduction, and whether it is the one that writes it
+    const uint32_t my_col = NS >= 4 ? (((s & (NS / 2)) ? 2u : 0u) + ((s & (NS / 4)) ? 1u : 0u)) : 0u;
+    const bool writer = NS >= 4 ? (s & (NS / 4 - 1)) == 0 : s == 0;
 
     auto fetch_tile = [&](uint32_t t0, uint32_t stage) {
         float* Bs = sm + stage * kStage;
@@ -79,26 +86,23 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
                 ssm_copy16(Bs + tt * NP + n, on ? bsrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
                 ssm_copy16(Cs + tt * NP + n, on ? csrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
             }
-            if (CP >= 4) {
-                for (uint32_t e = tid; e < nt * (XP / 4); e += kSsmThreads) {
-                    const uint32_t tt = e / (XP / 4), c = 4 * (e % (XP / 4));
-                    const bool on = c < x_cols;
-                    ssm_copy16(Xs + tt * XP + c, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
-                }
-                return;
+            for (uint32_t e = tid; e < nt * (CPB / 4); e += kSsmThreads) {
+                const uint32_t tt = e / (CPB / 4), c = 4 * (e % (CPB / 4));
+                const bool on = c < x_cols;
+                ssm_copy16(Xs + tt * CPB + c, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
             }
-        } else {
-            for (uint32_t e = tid; e < nt * NP; e += kSsmThreads) {
-                const uint32_t tt = e / NP, n = e % NP;
-                const bool on = n < a.N;
-                ssm_copy4(Bs + e, on ? bsrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
-                ssm_copy4(Cs + e, on ? csrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
-            }
+            return;
         }
-        for (uint32_t e = tid; e < nt * CP; e += kSsmThreads) {
-            const uint32_t tt = e / CP, c = e % CP;
+        for (uint32_t e = tid; e < nt * NP; e += kSsmThreads) {
+            const uint32_t tt = e / NP, n = e % NP;
+            const bool on = n < a.N;
+            ssm_copy4(Bs + e, on ? bsrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
+            ssm_copy4(Cs + e, on ? csrc + (size_t)(t0 + tt) * a.xbc_rs + n : a.xbc, on);
+        }
+        for (uint32_t e = tid; e < nt * CPB; e += kSsmThreads) {
+            const uint32_t tt = e / CPB, c = e % CPB;
             const bool on = c < x_cols;
-            ssm_copy4(Xs + tt * XP + c, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
+            ssm_copy4(Xs + e, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
         }
     };
     for (uint32_t base = 0; base < a.T; base += kSsmSpan) {
@@ -121,45 +125,91 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
             const float* Cs = Bs + kSsmTile * NP;
             const float* Xs = Cs + kSsmTile * NP;
             const uint32_t nt = min((uint32_t)kSsmTile, span - t0);
-            for (uint32_t tt = 0; tt < nt; tt++) {
-                const float x = Xs[tt * XP + pl], dec = Dec[t0 + tt], dtx = Dt[t0 + tt] * x;
-                float y = 0.0f;
+            constexpr int U = RQ > 1 ? 2 : 4;              // tokens per trip
+            for (uint32_t tt = 0; tt < nt; tt += U) {
+                float4 x[U];
+                float dec[U], dt[U];
+                float2 y[U][2];
 #pragma unroll
-                for (int q = 0; q < RP / 4; q++) {
-                    const float4 b = *reinterpret_cast<const float4*>(Bs + tt * NP + 4 * (s + NS * q));
-                    const float4 c = *reinterpret_cast<const float4*>(Cs + tt * NP + 4 * (s + NS * q));
-                    S[4 * q + 0] = fmaf(dec, S[4 * q + 0], dtx * b.x);
-                    S[4 * q + 1] = fmaf(dec, S[4 * q + 1], dtx * b.y);
-                    S[4 * q + 2] = fmaf(dec, S[4 * q + 2], dtx * b.z);
-                    S[4 * q + 3] = fmaf(dec, S[4 * q + 3], dtx * b.w);
-                    y = fmaf(S[4 * q + 0], c.x, fmaf(S[4 * q + 1], c.y, fmaf(S[4 * q + 2], c.z, fmaf(S[4 * q + 3], c.w, y))));
+                for (int u = 0; u < U; u++) {
+                    const uint32_t tu = min(tt + u, nt - 1);       // a token past the tile's end repeats the last one with decay 1 and step 0: the state stays
+                    const bool live = tt + u < nt;
+                    x[u] = *reinterpret_cast<const float4*>(Xs + tu * CPB + pl * 4);
+                    dec[u] = live ? Dec[t0 + tu] : 1.0f;
+                    dt[u] = live ? Dt[t0 + tu] : 0.0f;
+                    y[u][0] = y[u][1] = make_float2(0.0f, 0.0f);
                 }
 #pragma unroll
-                for (uint32_t o = NS / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-                if (s == 0 && col_ok) a.dst[(size_t)(base + t0 + tt) * a.H * a.P + (size_t)h * a.P + p] = fmaf(dsk, x, y);
+                for (int q = 0; q < RQ; q++) {
+                    float4 b[U], c[U];
+#pragma unroll
+                    for (int u = 0; u < U; u++) {
+                        const uint32_t tu = min(tt + u, nt - 1);
+                        b[u] = *reinterpret_cast<const float4*>(Bs + tu * NP + 4 * (s + NS * q));
+                        c[u] = *reinterpret_cast<const float4*>(Cs + tu * NP + 4 * (s + NS * q));
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; u++) {          // two columns per instruction: S = dec S + (dt B) x, y += S C
+                        const float bv[4] = {b[u].x * dt[u], b[u].y * dt[u], b[u].z * dt[u], b[u].w * dt[u]};
+                        const float cv[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+                        const float2 xp[2] = {make_float2(x[u].x, x[u].y), make_float2(x[u].z, x[u].w)};
+                        const float2 d2 = make_float2(dec[u], dec[u]);
+#pragma unroll
+                        for (int r = 0; r < 4; r++) {
+                            const float2 b2 = make_float2(bv[r], bv[r]), c2 = make_float2(cv[r], cv[r]);
+#pragma unroll
+                            for (int j = 0; j < 2; j++) {
+                                S[q][r][j] = __ffma2_rn(d2, S[q][r][j], __fmul2_rn(b2, xp[j]));
+                                y[u][j] = __ffma2_rn(S[q][r][j], c2, y[u][j]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    float k;
+                    const float yv[4] = {y[u][0].x, y[u][0].y, y[u][1].x, y[u][1].y};
+                    if (NS >= 4) {                         // scatter: after two steps a lane carries one column, then a plain butterfly
+                        const bool up = (s & (NS / 2)) != 0, up2 = (s & (NS / 4)) != 0;
+                        const float r0 = __shfl_xor_sync(0xffffffffu, up ? yv[0] : yv[2], NS / 2);
+                        const float r1 = __shfl_xor_sync(0xffffffffu, up ? yv[1] : yv[3], NS / 2);
+                        const float k0 = (up ? yv[2] : yv[0]) + r0, k1 = (up ? yv[3] : yv[1]) + r1;
+                        k = (up2 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, up2 ? k0 : k1, NS / 4);
+#pragma unroll
+                        for (uint32_t o = NS / 8; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
+                        const float xs = my_col == 0 ? x[u].x : (my_col == 1 ? x[u].y : (my_col == 2 ? x[u].z : x[u].w));
+                        if (writer && tt + u < nt && p0 + my_col < a.P) a.dst[(size_t)(base + t0 + tt + u) * a.H * a.P + (size_t)h * a.P + p0 + my_col] = fmaf(dsk, xs, k);
+                    } else {
+                        const float xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            k = yv[j];
+                            if (NS == 2) k += __shfl_xor_sync(0xffffffffu, k, 1);
+                            if (writer && tt + u < nt && p0 + j < a.P) a.dst[(size_t)(base + t0 + tt + u) * a.H * a.P + (size_t)h * a.P + p0 + j] = fmaf(dsk, xv[j], k);
+                        }
+                    }
+                }
             }
         }
     }
 #pragma unroll
-    for (int i = 0; i < RP; i++) st[i * kSsmThreads + tid] = S[i];
+    for (int i = 0; i < 8 * RQ; i++) {
+        st[(2 * i) * kSsmThreads + tid] = S[i / 8][(i / 2) % 4][i % 2].x;
+        st[(2 * i + 1) * kSsmThreads + tid] = S[i / 8][(i / 2) % 4][i % 2].y;
+    }
 }
 static size_t ssm_state_elems(uint32_t H, uint32_t N, uint32_t P) {
-    const uint32_t CP = kSsmThreads / ssm_slices(N);
-    return (size_t)H * ((P + CP - 1) / CP) * ssm_rows(N) * kSsmThreads;
+    const uint32_t CPB = kSsmThreads / ssm_slices(N) * 4;
+    return (size_t)H * ((P + CPB - 1) / CPB) * 16 * ssm_rq(N) * kSsmThreads;
 }
 
 // ── MIN_GRU ──────────────────────────────────────────────────────────────────────────────────────────────────────
 // S_t = (1 - z_t) S_{t-1} + z_t c_t is a linear recurrence per channel whose coefficients do not depend on the state, so the
-// step's tokens are cut into up to 32 segments that are walked side by side: thread (channel, segment) first walks its segment
+// step's tokens are cut into up to 64 segments that are walked side by side: thread (channel, segment) first walks its segment
 // from an empty state, keeping the product of the (1 - z) and the value reached; the segments' (product, value) pairs are then
 // folded in order, which gives every segment the state it starts from; the second walk writes the outputs.  A single-token
 // step is one segment of one token.
-constexpr int kGruChannels = 32, kGruMaxSegments = 32;
-__device__ __forceinline__ void gru_terms(const float* row, uint32_t z_off, uint32_t u_off, uint32_t c, float& z, float& cand) {
-    const float u = row[u_off + c];
-    z = sigmoidf_(row[z_off + c]);
-    cand = u >= 0.0f ? u + 0.5f : sigmoidf_(u);
-}
+constexpr int kGruChannels = 16, kGruMaxSegments = 64;
 __global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_min_gru(float* __restrict__ dst, const float* __restrict__ proj, float* __restrict__ state,
                                                                             const float* __restrict__ ctl, uint32_t T, uint32_t W, uint32_t rs, uint32_t drs,
                                                                             uint32_t z_off, uint32_t u_off, uint32_t g_off, uint32_t seg_len) {
@@ -170,14 +220,26 @@ __global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_min_gru(floa
     const uint32_t t_begin = min(T, seg * seg_len), t_end = min(T, t_begin + seg_len);
     float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * W;
     float S = 0.0f;
+    constexpr int U = 8;                                   // tokens whose loads are in flight together
     if (n_seg > 1) {
         float A = 1.0f;
         if (on)
-            for (uint32_t t = t_begin; t < t_end; t++) {
-                float z, cand;
-                gru_terms(proj + (size_t)t * rs, z_off, u_off, c, z, cand);
-                A *= 1.0f - z;
-                S = fmaf(z, cand, (1.0f - z) * S);
+            for (uint32_t t = t_begin; t < t_end; t += U) {
+                float zl[U], u[U];
+#pragma unroll
+                for (int i = 0; i < U; i++) {
+                    const float* row = proj + (size_t)min(t + i, t_end - 1) * rs;
+                    zl[i] = row[z_off + c];
+                    u[i] = row[u_off + c];
+                }
+#pragma unroll
+                for (int i = 0; i < U; i++) {
+                    if (t + i < t_end) {
+                        const float z = sigmoidf_(zl[i]), cand = u[i] >= 0.0f ? u[i] + 0.5f : sigmoidf_(u[i]);
+                        A *= 1.0f - z;
+                        S = fmaf(z, cand, (1.0f - z) * S);
+                    }
+                }
             }
         segA[seg][threadIdx.x] = A;
         segB[seg][threadIdx.x] = S;
@@ -186,13 +248,23 @@ __global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_min_gru(floa
     if (!on) return;
     S = st[c];
     for (uint32_t j = 0; j < seg; j++) S = fmaf(segA[j][threadIdx.x], S, segB[j][threadIdx.x]);
-    for (uint32_t t = t_begin; t < t_end; t++) {
-        const float* row = proj + (size_t)t * rs;
-        float z, cand;
-        gru_terms(row, z_off, u_off, c, z, cand);
-        const float gl = row[g_off + c];
-        S = fmaf(z, cand, (1.0f - z) * S);
-        dst[(size_t)t * drs + c] = S * (gl * sigmoidf_(gl));
+    for (uint32_t t = t_begin; t < t_end; t += U) {
+        float zl[U], u[U], gl[U];
+#pragma unroll
+        for (int i = 0; i < U; i++) {
+            const float* row = proj + (size_t)min(t + i, t_end - 1) * rs;
+            zl[i] = row[z_off + c];
+            u[i] = row[u_off + c];
+            gl[i] = row[g_off + c];
+        }
+#pragma unroll
+        for (int i = 0; i < U; i++) {
+            if (t + i < t_end) {
+                const float z = sigmoidf_(zl[i]), cand = u[i] >= 0.0f ? u[i] + 0.5f : sigmoidf_(u[i]);
+                S = fmaf(z, cand, (1.0f - z) * S);
+                dst[(size_t)(t + i) * drs + c] = S * (gl[i] * sigmoidf_(gl[i]));
+            }
+        }
     }
     if (seg == n_seg - 1) st[c] = S;
 }
@@ -206,13 +278,34 @@ __global__ void k_gated_norm(float* dst, const float* src, const float* __restri
     const uint32_t t = blockIdx.x / groups, gi = blockIdx.x % groups, gs = cols / groups, c0 = gi * gs;
     const float* x = src + (size_t)t * src_rs + c0;
     const float* gt = gate + (size_t)t * gate_rs + c0;
+    float* out = dst + (size_t)t * dst_rs + c0;
+    constexpr int kKeep = 8;                               // values a thread keeps: groups of up to 8 x blockDim are read once, all loads in flight together
+    if (gs <= kKeep * blockDim.x) {
+        float v[kKeep], z[kKeep], wv[kKeep];
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            v[i] = c < gs ? x[c] : 0.0f;
+            z[i] = c < gs ? gt[c] : 0.0f;
+            wv[i] = c < gs ? wld(w, c0 + c) : 0.0f;
+        }
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) { v[i] *= z[i] * sigmoidf_(z[i]); q = fmaf(v[i], v[i], q); }
+        const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)gs + eps);
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            const uint32_t c = threadIdx.x + i * blockDim.x;
+            if (c < gs) out[c] = v[i] * inv * wv[i];
+        }
+        return;
+    }
     float q = 0.0f;
     for (uint32_t c = threadIdx.x; c < gs; c += blockDim.x) {
         const float z = gt[c], v = x[c] * (z * sigmoidf_(z));
         q = fmaf(v, v, q);
     }
     const float inv = 1.0f / sqrtf(block_sum(q, sh) / (float)gs + eps);
-    float* out = dst + (size_t)t * dst_rs + c0;
     for (uint32_t c = threadIdx.x; c < gs; c += blockDim.x) {
         const float z = gt[c], v = x[c] * (z * sigmoidf_(z));
         out[c] = v * inv * wld(w, c0 + c);
@@ -239,19 +332,28 @@ __global__ void k_head_norm(float* x, const WT* __restrict__ w, const float* __r
 }
 
 // ── ACTIVATION ───────────────────────────────────────────────────────────────────────────────────────────────────
+__device__ __forceinline__ float activation(float z, uint32_t kind) {
+    switch (kind) {
+        case 0: { const float r = fmaxf(z, 0.0f); return r * r; }
+        case 1: return z * sigmoidf_(z);
+        case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+        default: return fmaxf(z, 0.0f);
+    }
+}
+// four elements per thread (n a multiple of 4, both buffers on 16-byte boundaries) or one
+template <bool VEC>
 __global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t kind) {
     pdl_enter();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= n) return;
-    const float z = src[e];
-    float y;
-    switch (kind) {
-        case 0: { const float r = fmaxf(z, 0.0f); y = r * r; break; }
-        case 1: y = z * sigmoidf_(z); break;
-        case 2: y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z))); break;
-        default: y = fmaxf(z, 0.0f); break;
+    if (VEC) {
+        if (4 * e >= n) return;
+        float4 v = reinterpret_cast<const float4*>(src)[e];
+        v.x = activation(v.x, kind); v.y = activation(v.y, kind); v.z = activation(v.z, kind); v.w = activation(v.w, kind);
+        reinterpret_cast<float4*>(dst)[e] = v;
+    } else {
+        if (e >= n) return;
+        dst[e] = activation(src[e], kind);
     }
-    dst[e] = y;
 }
 
 }  // namespace
@@ -326,26 +428,27 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
             a.dst = bufs[s.buf[0]]; a.xbc = bufs[s.buf[1]]; a.dtl = bufs[s.buf[2]]; a.state = bufs[s.buf[4]]; a.ctl = bufs[s.buf[5]];
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.N = s.n[3]; a.P = s.n[4]; a.x_off = s.off[0]; a.b_off = s.off[1]; a.c_off = s.off[2]; a.dt_off = s.off[3];
             a.xbc_rs = s.n[5]; a.dt_rs = s.n[6];
-            const uint32_t NS = ssm_slices(a.N), RP = ssm_rows(a.N), CP = kSsmThreads / NS, XP = (CP + 3) & ~3u;
+            const uint32_t NS = ssm_slices(a.N), RQ = ssm_rq(a.N), CPB = kSsmThreads / NS * 4;
             // 16-byte copies when every row of B, C and the CTA's x columns starts on a 16-byte boundary
             a.vec = (a.N % 4 == 0 && a.P % 4 == 0 && a.xbc_rs % 4 == 0 && a.x_off % 4 == 0 && a.b_off % 4 == 0 && a.c_off % 4 == 0 &&
                      (reinterpret_cast<uintptr_t>(a.xbc) & 15) == 0) ? 1u : 0u;
-            const dim3 grid((a.P + CP - 1) / CP, a.H);
-            const size_t smem = ((size_t)2 * kSsmTile * (2 * NS * RP + XP) + 2 * kSsmSpan) * sizeof(float);
-#define ZG_SSM(NS_, RP_)                                                                                                                  \
+            const dim3 grid((a.P + CPB - 1) / CPB, a.H);
+            const size_t smem = ((size_t)2 * kSsmTile * (2 * NS * 4 * RQ + CPB) + 2 * kSsmSpan) * sizeof(float);
+#define ZG_SSM(NS_, RQ_)                                                                                                                  \
     ZG_SEQ_WDT(s.n[7], {                                                                                                                  \
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_, RP_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-        launch_pdl(k_ssm_scan<WT, NS_, RP_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_, RQ_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        launch_pdl(k_ssm_scan<WT, NS_, RQ_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
                    wptr<WT>(bufs, s.buf[3], s.off[6]));                                                                                   \
     })
-            if (RP == 16) ZG_SSM(32, 16);
+            if (RQ == 4) ZG_SSM(32, 4);
+            else if (RQ == 2) ZG_SSM(32, 2);
             else switch (NS) {
-                case 1: ZG_SSM(1, 8); break;
-                case 2: ZG_SSM(2, 8); break;
-                case 4: ZG_SSM(4, 8); break;
-                case 8: ZG_SSM(8, 8); break;
-                case 16: ZG_SSM(16, 8); break;
-                default: ZG_SSM(32, 8); break;
+                case 1: ZG_SSM(1, 1); break;
+                case 2: ZG_SSM(2, 1); break;
+                case 4: ZG_SSM(4, 1); break;
+                case 8: ZG_SSM(8, 1); break;
+                case 16: ZG_SSM(16, 1); break;
+                default: ZG_SSM(32, 1); break;
             }
 #undef ZG_SSM
             ZG_SEQ_CHECK();
@@ -364,7 +467,7 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
         }
         case ZG_OP_GATED_NORM: {
             const uint32_t gs = s.n[1] / s.n[2];
-            const uint32_t threads = gs <= 64 ? 32 : (gs <= 512 ? 128 : 256);
+            const uint32_t threads = gs <= 64 ? 32 : (gs <= 512 ? 128 : (gs <= 2048 ? 256 : 512));
             ZG_SEQ_WDT(s.n[4], launch_pdl(k_gated_norm<WT>, dim3(s.n[0] * s.n[2]), dim3(threads), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]] + s.off[0],
                                           wptr<WT>(bufs, s.buf[3], s.off[1]), s.n[1], s.n[2], s.n[3], s.n[5], s.n[6], s.f[0]));
             ZG_SEQ_CHECK();
@@ -378,7 +481,10 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
             return true;
         }
         case ZG_OP_ACTIVATION:
-            launch_pdl(k_activation, dim3((s.n[0] + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], s.n[0], s.n[1]);
+            if (s.n[0] % 4 == 0 && ((reinterpret_cast<uintptr_t>(bufs[s.buf[0]]) | reinterpret_cast<uintptr_t>(bufs[s.buf[1]])) & 15) == 0)
+                launch_pdl(k_activation<true>, dim3((s.n[0] / 4 + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], (const float*)bufs[s.buf[1]], s.n[0], s.n[1]);
+            else
+                launch_pdl(k_activation<false>, dim3((s.n[0] + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], (const float*)bufs[s.buf[1]], s.n[0], s.n[1]);
             ZG_SEQ_CHECK();
             return true;
         default:

@@ -21,6 +21,7 @@ __global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, 
     const size_t row = (size_t)ctl_word(ctl, ZG_CTL_IDS + t) * D;
     if (positions) {       // a learned position row, not scaled
         const size_t prow = ((size_t)ctl_word(ctl, ZG_CTL_POS) + t) * D;
+#pragma unroll 4
         for (uint32_t c = threadIdx.x; c < D; c += blockDim.x) dst[(size_t)t * D + c] = fmaf(wld(table, row + c), scale, wld(positions, prow + c));
         return;
     }
@@ -301,43 +302,126 @@ __global__ void k_norm(float* __restrict__ dst, const float* __restrict__ src, c
     }
 }
 
-// Kinds without row statistics (Dynamic Tanh; the plain residual step) and their combinations with the others: one CTA per row,
-// nothing cached.  dst = (res +) f(src) and, with dst2, dst2 = f2(dst): the residual step that closes a sublayer and the
-// Dynamic Tanh that opens the next are one launch.
+// Kinds without row statistics (Dynamic Tanh; the plain residual step), their combinations with the others, and the sum of TWO
+// normed sources: one CTA per row.  dst = (res +) f(src) (+ f_b(src_b)) and, with dst2, dst2 = f2(dst): the residual step that
+// closes a sublayer and the Dynamic Tanh that opens the next are one launch.  Rows of up to kNormCache x blockDim values live in
+// registers: weights and biases are constants of the model and are read BEFORE the wait on the predecessor, the row, its
+// residual and the second source together right after it.  Wider rows are walked from memory.
+template <typename WT>
+__device__ __forceinline__ float norm_any_value(float x, float mean, float inv, float w, float aux, uint32_t kind, float gain, float alpha) {
+    const float g = (kind & 4u) ? gain : 1.0f;
+    if (kind & 16u) return x * g;
+    if (kind & 8u) return fmaf(tanhf(alpha * x), w, aux) * g;
+    return (x - mean) * inv * ((kind & 2u) ? w + 1.0f : w) * g;
+}
 template <typename WT>
 __device__ void norm_any_pass(float* out, const float* x, const float* res, const WT* __restrict__ w, uint32_t cols, uint32_t kind, float eps, float gain,
-                              float* sh) {
-    float mean = 0.0f, inv = 1.0f;
+                              float* sh, const float* xb, const WT* __restrict__ wb) {
+    float mean = 0.0f, inv = 1.0f, mean_b = 0.0f, inv_b = 1.0f;
     if (!(kind & 24u)) {
         if (!(kind & 1u)) {
-            float sum = 0.0f;
-            for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) sum += x[c];
+            float sum = 0.0f, sum_b = 0.0f;
+            for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { sum += x[c]; if (xb) sum_b += xb[c]; }
             mean = block_sum(sum, sh) / (float)cols;
+            if (xb) mean_b = block_sum(sum_b, sh) / (float)cols;
         }
-        float q = 0.0f;
-        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) { const float d = x[c] - mean; q = fmaf(d, d, q); }
+        float q = 0.0f, qb = 0.0f;
+        for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float d = x[c] - mean; q = fmaf(d, d, q);
+            if (xb) { const float e = xb[c] - mean_b; qb = fmaf(e, e, qb); }
+        }
         inv = 1.0f / sqrtf(block_sum(q, sh) / (float)cols + eps);
+        if (xb) inv_b = 1.0f / sqrtf(block_sum(qb, sh) / (float)cols + eps);
     }
-    const float g = (kind & 4u) ? gain : 1.0f;
     const float alpha = (kind & 8u) ? wld(w, (size_t)2 * cols) : 0.0f;
     for (uint32_t c = threadIdx.x; c < cols; c += blockDim.x) {
-        float y;
-        if (kind & 16u) y = x[c] * g;
-        else if (kind & 8u) y = fmaf(tanhf(alpha * x[c]), wld(w, c), wld(w, (size_t)cols + c)) * g;
-        else y = (x[c] - mean) * inv * norm_weight(wld(w, c), kind, gain);
+        float y = norm_any_value<WT>(x[c], mean, inv, (kind & 16u) ? 0.0f : wld(w, c), (kind & 8u) ? wld(w, (size_t)cols + c) : 0.0f, kind, gain, alpha);
+        if (xb) y += norm_any_value<WT>(xb[c], mean_b, inv_b, wld(wb, c), 0.0f, kind, gain, 0.0f);
         out[c] = res ? res[c] + y : y;
     }
 }
+// many rows (prompts): what counts is how many rows are resident per SM, so nothing is kept in registers
 template <typename WT>
-__global__ void k_norm_any(float* dst, const float* src, const WT* __restrict__ w, const float* res, uint32_t cols, uint32_t kind, float eps,
-                           float* dst2, const WT* __restrict__ w2, uint32_t kind2, float gain) {
+__global__ void __launch_bounds__(256) k_norm_any_rows(float* dst, const float* src, const WT* __restrict__ w, const float* res, uint32_t cols, uint32_t kind, float eps,
+                                                       float* dst2, const WT* __restrict__ w2, uint32_t kind2, float gain, const float* src_b, const WT* __restrict__ w_b) {
     pdl_enter();
     __shared__ float sh[32];
     const size_t row = (size_t)blockIdx.x * cols;
-    norm_any_pass(dst + row, src + row, res ? res + row : nullptr, w, cols, kind, eps, gain, sh);
+    norm_any_pass(dst + row, src + row, res ? res + row : nullptr, w, cols, kind, eps, gain, sh, src_b ? src_b + row : nullptr, w_b);
     if (dst2) {
-        __syncthreads();                               // the row just written is read back by other threads
-        norm_any_pass(dst2 + row, dst + row, (const float*)nullptr, w2, cols, kind2, eps, gain, sh);
+        __syncthreads();                                   // the row just written is read back by other threads
+        norm_any_pass(dst2 + row, dst + row, (const float*)nullptr, w2, cols, kind2, eps, gain, sh, (const float*)nullptr, (const WT*)nullptr);
+    }
+}
+template <typename WT, int kKeep, int kThreads>          // a row of up to kKeep x kThreads values lives in registers (fewer kept values, more CTAs per SM)
+__global__ void __launch_bounds__(kThreads) k_norm_any(float* dst, const float* src, const WT* __restrict__ w, const float* res, uint32_t cols, uint32_t kind, float eps,
+                                                  float* dst2, const WT* __restrict__ w2, uint32_t kind2, float gain, const float* src_b, const WT* __restrict__ w_b) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ float sh[32];
+    const size_t row = (size_t)blockIdx.x * cols;
+    if (cols > kKeep * kThreads) {                  // rows too wide for the registers
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        norm_any_pass(dst + row, src + row, res ? res + row : nullptr, w, cols, kind, eps, gain, sh, src_b ? src_b + row : nullptr, w_b);
+        if (dst2) {
+            __syncthreads();                               // the row just written is read back by other threads
+            norm_any_pass(dst2 + row, dst + row, (const float*)nullptr, w2, cols, kind2, eps, gain, sh, (const float*)nullptr, (const WT*)nullptr);
+        }
+        return;
+    }
+    float v[kKeep], wa[kKeep], aux[kKeep], wc[kKeep], bc[kKeep];   // aux: the bias of a Dynamic Tanh, or the second source's weight
+#pragma unroll
+    for (int i = 0; i < kKeep; i++) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        const bool in = c < cols;
+        wa[i] = (in && !(kind & 16u)) ? wld(w, c) : 0.0f;
+        aux[i] = in ? ((kind & 8u) ? wld(w, (size_t)cols + c) : (src_b ? wld(w_b, c) : 0.0f)) : 0.0f;
+        wc[i] = (in && dst2 && !(kind2 & 16u)) ? wld(w2, c) : 0.0f;
+        bc[i] = (in && dst2 && (kind2 & 8u)) ? wld(w2, (size_t)cols + c) : 0.0f;
+    }
+    const float alpha = (kind & 8u) ? wld(w, (size_t)2 * cols) : 0.0f, alpha2 = (dst2 && (kind2 & 8u)) ? wld(w2, (size_t)2 * cols) : 0.0f;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float rv[kKeep], vb[kKeep];
+#pragma unroll
+    for (int i = 0; i < kKeep; i++) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        v[i] = c < cols ? src[row + c] : 0.0f;
+        rv[i] = (res && c < cols) ? res[row + c] : 0.0f;
+        vb[i] = (src_b && c < cols) ? src_b[row + c] : 0.0f;
+    }
+    auto stats = [&](const float (&val)[kKeep], uint32_t k, float& mean, float& inv) {
+        mean = 0.0f; inv = 1.0f;
+        if (k & 24u) return;
+        if (!(k & 1u)) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kKeep; i++) sum += val[i];
+            mean = block_sum(sum, sh) / (float)cols;
+        }
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            const float d = threadIdx.x + i * blockDim.x < cols ? val[i] - mean : 0.0f;
+            q = fmaf(d, d, q);
+        }
+        inv = 1.0f / sqrtf(block_sum(q, sh) / (float)cols + eps);
+    };
+    float mean, inv, mean_b = 0.0f, inv_b = 1.0f;
+    stats(v, kind, mean, inv);
+    if (src_b) stats(vb, kind, mean_b, inv_b);
+#pragma unroll
+    for (int i = 0; i < kKeep; i++) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        float y = norm_any_value<WT>(v[i], mean, inv, wa[i], aux[i], kind, gain, alpha);
+        if (src_b) y += norm_any_value<WT>(vb[i], mean_b, inv_b, aux[i], 0.0f, kind, gain, 0.0f);
+        v[i] = res ? rv[i] + y : y;
+        if (c < cols) dst[row + c] = v[i];
+    }
+    if (!dst2) return;
+    stats(v, kind2, mean, inv);
+#pragma unroll
+    for (int i = 0; i < kKeep; i++) {
+        const uint32_t c = threadIdx.x + i * blockDim.x;
+        if (c < cols) dst2[row + c] = norm_any_value<WT>(v[i], mean, inv, wc[i], bc[i], kind2, gain, alpha2);
     }
 }
 
@@ -1341,7 +1425,11 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!n || s.n[2] > 31 || (s.n[2] & 24u) == 24u) return fail("norm: shape");
             const size_t w_need = (s.n[2] & 8u) ? 2 * (size_t)s.n[1] + 1 : s.n[1];      // Dynamic Tanh: weight, bias and alpha
             if (!fits(0, s.off[3], n) || !fits(1, 0, n) || (!(s.n[2] & 16u) && !wfits(2, s.off[0], w_need))) return fail("norm: extent");
-            if (((s.n[2] | (s.buf[4] != ZG_NO_BUF && !s.n[5] ? s.n[4] : 0u)) & 24u) && (s.n[5] || s.buf[6] != ZG_NO_BUF)) return fail("norm: kinds without statistics take no averaged source and no token shift");
+            if (s.n[7]) {      // a second source, normed like the first with its own weight (off 2 of w's arena) and added to it
+                if (s.n[7] > 1 || (s.n[2] & 24u) || s.n[5] || !fits(6, 0, n) || !wfits(2, s.off[2], s.n[1]) || s.buf[6] == s.buf[0] || (s.buf[4] != ZG_NO_BUF && s.buf[6] == s.buf[4]))
+                    return fail("norm: second source");
+            } else if (((s.n[2] | (s.buf[4] != ZG_NO_BUF && !s.n[5] ? s.n[4] : 0u)) & 24u) && (s.n[5] || s.buf[6] != ZG_NO_BUF))
+                return fail("norm: kinds without statistics take no averaged source and no token shift");
             if (s.n[5]) {      // averaged source
                 if (s.n[6] < n || !fits(1, 0, (size_t)(s.n[5] - 1) * s.n[6] + n) || !wfits(2, s.off[4], s.n[5]) || s.buf[3] != ZG_NO_BUF || !fits(4, 0, n) || s.buf[4] == s.buf[0] ||
                     s.buf[4] == s.buf[1])
@@ -1352,7 +1440,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (s.buf[3] != ZG_NO_BUF && !fits(3, 0, n)) return fail("norm: residual extent");
             if (s.buf[4] != ZG_NO_BUF && (s.n[4] > 31 || (s.n[4] & 24u) == 24u || !fits(4, 0, n) || (!(s.n[4] & 16u) && !wfits(5, s.off[1], (s.n[4] & 8u) ? 2 * (size_t)s.n[1] + 1 : s.n[1])) || s.buf[4] == s.buf[0] || s.buf[4] == s.buf[1] || s.buf[4] == s.buf[3]))
                 return fail("norm: chained norm");
-            if (s.buf[6] != ZG_NO_BUF && (s.n[0] != 1 || !have(6) || elems[s.buf[6]] < s.n[1] || !wfits(s.buf[4] != ZG_NO_BUF ? 5 : 2, s.off[2], s.n[1]) || !fits(7, 0, ZG_CTL_IDS)))
+            if (!s.n[7] && s.buf[6] != ZG_NO_BUF && (s.n[0] != 1 || !have(6) || elems[s.buf[6]] < s.n[1] || !wfits(s.buf[4] != ZG_NO_BUF ? 5 : 2, s.off[2], s.n[1]) || !fits(7, 0, ZG_CTL_IDS)))
                 return fail("norm: fused token shift (single-row steps)");
             return true;
         }
@@ -1485,10 +1573,21 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             float* dst2 = s.buf[4] != ZG_NO_BUF ? bufs[s.buf[4]] : nullptr;
             float* shift_state = s.buf[6] != ZG_NO_BUF ? bufs[s.buf[6]] : nullptr;
             const uint32_t avg_terms = s.n[5];             // averaged source: buf 4 receives the average instead of a chained norm
-            if ((s.n[2] | (dst2 ? s.n[4] : 0u)) & 24u) {   // Dynamic Tanh or the plain residual step somewhere in the launch
-                ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm_any<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]] + s.off[3], (const float*)bufs[s.buf[1]],
-                                              (s.n[2] & 16u) ? (const WT*)nullptr : wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0], dst2,
-                                              dst2 && !(s.n[4] & 16u) ? wptr<WT>(bufs, s.buf[5], s.off[1]) : (const WT*)nullptr, s.n[4], s.f[1]));
+            if (((s.n[2] | (dst2 ? s.n[4] : 0u)) & 24u) || s.n[7]) {   // Dynamic Tanh or the plain residual step somewhere in the launch, or two sources
+#define ZG_NORM_ANY(KEEP_, THREADS_)                                                                                                               \
+    ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm_any<WT, KEEP_, THREADS_>, dim3(s.n[0]), dim3(THREADS_), 0, st, bufs[s.buf[0]] + s.off[3], (const float*)bufs[s.buf[1]], \
+                                  (s.n[2] & 16u) ? (const WT*)nullptr : wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0], dst2,                \
+                                  dst2 && !(s.n[4] & 16u) ? wptr<WT>(bufs, s.buf[5], s.off[1]) : (const WT*)nullptr, s.n[4], s.f[1],                         \
+                                  s.n[7] ? (const float*)bufs[s.buf[6]] : (const float*)nullptr, s.n[7] ? wptr<WT>(bufs, s.buf[2], s.off[2]) : (const WT*)nullptr))
+                if (s.n[0] >= 64 || s.n[1] > 4096)
+                    ZG_SEQ_WDT(s.n[3], launch_pdl(k_norm_any_rows<WT>, dim3(s.n[0]), dim3(256), 0, st, bufs[s.buf[0]] + s.off[3], (const float*)bufs[s.buf[1]],
+                                                  (s.n[2] & 16u) ? (const WT*)nullptr : wptr<WT>(bufs, s.buf[2], s.off[0]), res, s.n[1], s.n[2], s.f[0], dst2,
+                                                  dst2 && !(s.n[4] & 16u) ? wptr<WT>(bufs, s.buf[5], s.off[1]) : (const WT*)nullptr, s.n[4], s.f[1],
+                                                  s.n[7] ? (const float*)bufs[s.buf[6]] : (const float*)nullptr, s.n[7] ? wptr<WT>(bufs, s.buf[2], s.off[2]) : (const WT*)nullptr));
+                else if (s.n[1] <= 1024) ZG_NORM_ANY(4, 256);
+                else if (s.n[1] <= 2048) ZG_NORM_ANY(8, 256);
+                else ZG_NORM_ANY(8, 512);                      // up to 4096 columns in registers; wider rows are walked from memory
+#undef ZG_NORM_ANY
                 ZG_SEQ_CHECK();
                 return true;
             }

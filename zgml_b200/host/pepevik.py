@@ -19,7 +19,7 @@ parallel    [q | k | v | z | u | g] = W h + b in ONE matmul for both branches.  
             temperature), CACHE_APPEND norms the key heads on their way into the cache, CACHED_ATTENTION with sigmoid weights;
             the distance penalty and the per-head score bias are ONE table per layer, pb_h - r1_h ln(1 + r2_h d), evaluated in
             f32 at load for every distance the cache can hold.  Right: MIN_GRU.  Each branch has its own W_o; the two RMS
-            norms of the results are residual steps of half the multiplier each.
+            norms of the results and their sum are one residual step with two sources.
 feed-forward dense: W_up, ACTIVATION relu^2, W_down.  moe: router matmul, ROUTE "corrected_sigmoid" with groups, MOE_FFN.
 """
 import json
@@ -303,14 +303,15 @@ class PepevikModel:
         x = xs[0]
         ops.append(DeviceOp.embed(x, ctl, gl, GA.off["embed"], T, D, cfg.embedding_scale, wdt, positions_off=GA.off["pos"]))
         # The residual step that closes a sublayer waits for the Dynamic Tanh that opens the next one: one launch for both.
-        pending: List[tuple] = []          # (src, kind, weight buffer, weight offset, gain): x += gain * kind(src)
+        pending: List[tuple] = []          # (src, kind, weight buffer, weight offset, gain, second source, its weight offset): x += gain * kind(src ...)
 
         def open_norm(dst, wb, w_off):
             nonlocal x
             if pending:
-                src, kind, pw, p_off, gain = pending.pop()
+                src, kind, pw, p_off, gain, src2, p2_off = pending.pop()
                 nx = next_x(x)
-                ops.append(DeviceOp.norm(nx, src, pw, p_off, T, D, eps, wdt, kind=kind, res=x, gain=gain, then=dst, then_w=wb, then_w_off=w_off, then_kind="dyt"))
+                ops.append(DeviceOp.norm(nx, src, pw, p_off, T, D, eps, wdt, kind=kind, res=x, gain=gain, then=dst, then_w=wb, then_w_off=w_off, then_kind="dyt",
+                                         src2=src2, src2_w_off=p2_off))
                 x = nx
             else:
                 ops.append(DeviceOp.norm(dst, x, wb, w_off, T, D, eps, wdt, kind="dyt"))
@@ -318,9 +319,9 @@ class PepevikModel:
         def flush():
             nonlocal x
             if pending:
-                src, kind, pw, p_off, gain = pending.pop()
+                src, kind, pw, p_off, gain, src2, p2_off = pending.pop()
                 nx = next_x(x)
-                ops.append(DeviceOp.norm(nx, src, pw, p_off, T, D, eps, wdt, kind=kind, res=x, gain=gain))
+                ops.append(DeviceOp.norm(nx, src, pw, p_off, T, D, eps, wdt, kind=kind, res=x, gain=gain, src2=src2, src2_w_off=p2_off))
                 x = nx
 
         layer_bufs = []
@@ -345,7 +346,7 @@ class PepevikModel:
                                              A.off["A_log"], A.off["dt_bias"], A.off["D"], T, H, G, N, P, C, ni, wdt))
                 ops.append(DeviceOp.gated_norm(mix, mix, proj, wb, A.off["gnorm"], 0, T, inner, m["norm_groups"], ni, eps, wdt))
                 ops.append(DeviceOp.linear(y, mix, wb, A.off["o"], T, D, inner, wdt))
-                pending.append((y, "none", None, 0, mult))
+                pending.append((y, "none", None, 0, mult, None, 0))
             else:
                 l, W = m["left"], meta["W"]
                 H, G, dim, vdim = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
@@ -364,11 +365,8 @@ class PepevikModel:
                 yr = scratch("right", TD)
                 ops.append(DeviceOp.linear(y, att, wb, A.off["left.o"], T, D, H * vdim, wdt))
                 ops.append(DeviceOp.linear(yr, gru, wb, A.off["right.o"], T, D, W, wdt))
-                # half the sum of the two RMS-normed results, times the multiplier: two residual steps of half the multiplier each
-                nx = next_x(x)
-                ops.append(DeviceOp.norm(nx, y, wb, A.off["left.out"], T, D, eps, wdt, kind="rms", res=x, gain=0.5 * mult))
-                x = nx
-                pending.append((yr, "rms", wb, A.off["right.out"], 0.5 * mult))
+                # half the sum of the two RMS-normed results, times the multiplier: ONE residual step with two sources
+                pending.append((y, "rms", wb, A.off["left.out"], 0.5 * mult, yr, A.off["right.out"]))
             mlp = L["mlp"]
             if mlp is not None:
                 open_norm(h, wb, A.off["norm2"])
@@ -388,7 +386,7 @@ class PepevikModel:
                                               up_offset=0.0)
                     moe_op.u.seq.buf[4] = scratch("expert", seq_scratch_elems(moe_op))   # the library knows what its kernels stage
                     ops.append(moe_op)
-                pending.append((y, "none", None, 0, mult))
+                pending.append((y, "none", None, 0, mult, None, 0))
         logits, rows = None, 0
         if head != "none":
             open_norm(h, gl, GA.off["final.norm"])
