@@ -305,7 +305,7 @@ def test_far_key_among_hundreds(cuda_backend):
 
 
 @pytest.mark.parametrize("layer", [pair_layer(heads=4, kv_heads=2, dim=68, vdim=132, gru=24, every=50), pair_layer(heads=8, kv_heads=1, dim=4, vdim=4, gru=8, every=128),
-                                   pair_layer(heads=2, kv_heads=2, dim=96, vdim=96, gru=300, every=256)], ids=["wide", "8-per-group", "96"])
+                                   pair_layer(heads=2, kv_heads=2, dim=88, vdim=72, gru=300, every=200)], ids=["wide", "8-per-group", "88"])
 def test_long_cache_and_split_decoding(cuda_backend, layer):
     """Keys beyond one tile of the prompt kernel (64) and one share of the decoding kernel (32), key and value sizes beyond one
     slice, and a cache long enough that single-token steps deal their keys to several CTAs whose unnormalised shares add up."""

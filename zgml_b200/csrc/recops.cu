@@ -11,23 +11,24 @@ namespace {
 
 // ── SSM_SCAN ─────────────────────────────────────────────────────────────────────────────────────────────────────
 // Columns of a head's state S [N, P] evolve independently given the token's B, C, decay and step size, so a head is split by
-// columns over CTAs.  A thread keeps a block of 4 RQ state rows x 4 columns in registers: every B and C value it reads from
-// shared memory serves four columns and every x value four rows (one column per thread was bound by shared-memory
-// wavefronts, not by arithmetic).  The NS threads that share four columns sit in adjacent lanes (NS a power of two <= 32);
-// thread s owns rows 4 s + 4 NS q + i (q < RQ, i < 4), so the NS lanes read consecutive float4s of B and C.  Per token the
-// critical path is one FMA per state element, S = a S + (dt x) B.  The read-out sums of the four columns are reduced across
-// the NS lanes in a scatter: each step halves the columns a lane still carries, so four columns cost 6 shuffles, not 20.
+// columns over CTAs.  A thread keeps a block of 16 RQ state rows x 2 columns in registers (RQ = 1 / 2 / 4 for N <= 128 / 256 /
+// 512) as PAIRS OF ROWS: a float4 of B or C read from shared memory is two such pairs as it stands, so the update
+// S = a S + B (dt x) and the read-out y += S C are packed f32x2 instructions with no repacking, every B and C value serves
+// two columns, and most of the read-out sum stays inside the thread.  (One column and 8 rows per thread was bound by
+// shared-memory wavefronts; 4 x 4 blocks by instructions per state element: shuffles, selects and register moves.)  The NS
+// threads that share two columns sit in adjacent lanes (NS a power of two <= 8); thread s owns the float4s s + NS i (i < 4 RQ)
+// of the rows, so the NS lanes read consecutive float4s.  What is left of the read-out sum crosses the NS lanes in a scatter:
+// after the first step a lane carries one of the two columns.
 // Step sizes and decays of the head (softplus, two exponentials) are evaluated for a span of tokens at once, in parallel,
 // before the walk; B, C and the CTA's x columns arrive in tiles of kSsmTile tokens through cp.async, two tiles in flight, so
-// the next tile's loads run under this tile's walk; four tokens are walked per trip so that their loads, products and
-// reductions interleave.
-// State in memory: [H][column blocks][16 RQ][kSsmThreads], element (i, thread) — each thread's block, fully coalesced; the
+// the next tile's loads run under this tile's walk; two tokens are walked per trip so that their loads and sums interleave.
+// State in memory: [H][column blocks][32 RQ][kSsmThreads], element (i, thread) — each thread's block, fully coalesced; the
 // layout is private to the op (zeros mean an empty state in any layout).
 constexpr int kSsmThreads = 128, kSsmTile = 16, kSsmSpan = 1024, kSsmMaxN = 512;
 __host__ __device__ inline uint32_t ssm_rq(uint32_t N) { return N > 256 ? 4 : (N > 128 ? 2 : 1); }
 __host__ __device__ inline uint32_t ssm_slices(uint32_t N) {
     uint32_t ns = 1;
-    while (ns * 4 * ssm_rq(N) < N) ns <<= 1;
+    while (ns * 16 * ssm_rq(N) < N) ns <<= 1;
     return ns;
 }
 struct SsmArgs {
@@ -48,31 +49,31 @@ __device__ __forceinline__ void ssm_copy16(float* dst, const float* src, bool on
 template <typename WT, uint32_t NS, int RQ>
 __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* __restrict__ a_log, const WT* __restrict__ dt_bias, const WT* __restrict__ dskip) {
     pdl_enter();
-    constexpr uint32_t CPB = kSsmThreads / NS * 4, NP = NS * 4 * RQ;     // columns per CTA, padded state rows
+    constexpr uint32_t CPB = kSsmThreads / NS * 2, NP = NS * 16 * RQ, NI = 4 * RQ;   // columns per CTA, padded state rows, float4s of rows per thread
     extern __shared__ __align__(16) float sm[];
     constexpr uint32_t kStage = kSsmTile * (2 * NP + CPB);               // per stage: B [tile][NP], C [tile][NP], x [tile][CPB]
     float* Dt = sm + 2 * kStage;                                         // step sizes and decays of a span of tokens
     float* Dec = Dt + kSsmSpan;
     const uint32_t tid = threadIdx.x, s = tid % NS, pl = tid / NS;
     const uint32_t h = blockIdx.y, cb = blockIdx.x, g = h / (a.H / a.G);
-    const uint32_t p0 = cb * CPB + pl * 4;                               // this thread's first column
+    const uint32_t p0 = cb * CPB + pl * 2;                               // this thread's first column
     const uint32_t slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
     const uint32_t n_cb = (a.P + CPB - 1) / CPB;
-    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (16 * RQ * kSsmThreads);
-    float2 S[RQ][4][2];                                                  // [q][row][column pair]: two columns per register pair, for the packed f32x2 FMA
+    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (32 * RQ * kSsmThreads);
+    float2 S[NI][2][2];                                                  // [float4 of rows][pair of rows in it][column]
 #pragma unroll
-    for (int i = 0; i < 8 * RQ; i++) {
-        S[i / 8][(i / 2) % 4][i % 2].x = st[(2 * i) * kSsmThreads + tid];
-        S[i / 8][(i / 2) % 4][i % 2].y = st[(2 * i + 1) * kSsmThreads + tid];
+    for (int i = 0; i < 16 * RQ; i++) {
+        S[i / 4][(i / 2) % 2][i % 2].x = st[(2 * i) * kSsmThreads + tid];
+        S[i / 4][(i / 2) % 2][i % 2].y = st[(2 * i + 1) * kSsmThreads + tid];
     }
     const float neg_a = -expf(wld(a_log, h)), bias = wld(dt_bias, h), dsk = wld(dskip, h);
     const float* bsrc = a.xbc + a.b_off + (size_t)g * a.N;
     const float* csrc = a.xbc + a.c_off + (size_t)g * a.N;
     const float* xsrc = a.xbc + a.x_off + (size_t)h * a.P + (size_t)cb * CPB;
     const uint32_t x_cols = min(CPB, a.P - cb * CPB);
-    // which of its four columns the thread ends up with after the scattered reduction, and whether it is the one that writes it
-    const uint32_t my_col = NS >= 4 ? (((s & (NS / 2)) ? 2u : 0u) + ((s & (NS / 4)) ? 1u : 0u)) : 0u;
-    const bool writer = NS >= 4 ? (s & (NS / 4 - 1)) == 0 : s == 0;
+    // which of its two columns the thread ends up with after the scattered reduction, and whether it is the one that writes it
+    const bool up = NS >= 2 && (s & (NS / 2)) != 0;
+    const bool writer = NS >= 2 ? (s & (NS / 2 - 1)) == 0 : true;
 
     auto fetch_tile = [&](uint32_t t0, uint32_t stage) {
         float* Bs = sm + stage * kStage;
@@ -125,82 +126,65 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
             const float* Cs = Bs + kSsmTile * NP;
             const float* Xs = Cs + kSsmTile * NP;
             const uint32_t nt = min((uint32_t)kSsmTile, span - t0);
-            constexpr int U = RQ > 1 ? 2 : 4;              // tokens per trip
+            constexpr int U = 2;                           // tokens per trip
+            float* out = a.dst + (size_t)(base + t0) * a.H * a.P + (size_t)h * a.P + p0;
             for (uint32_t tt = 0; tt < nt; tt += U) {
-                float4 x[U];
-                float dec[U], dt[U];
-                float2 y[U][2];
+                float2 x[U], d2[U], tx[U][2], y[U][2];
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     const uint32_t tu = min(tt + u, nt - 1);       // a token past the tile's end repeats the last one with decay 1 and step 0: the state stays
                     const bool live = tt + u < nt;
-                    x[u] = *reinterpret_cast<const float4*>(Xs + tu * CPB + pl * 4);
-                    dec[u] = live ? Dec[t0 + tu] : 1.0f;
-                    dt[u] = live ? Dt[t0 + tu] : 0.0f;
+                    x[u] = *reinterpret_cast<const float2*>(Xs + tu * CPB + pl * 2);
+                    const float dec = live ? Dec[t0 + tu] : 1.0f, dt = live ? Dt[t0 + tu] : 0.0f;
+                    d2[u] = make_float2(dec, dec);
+                    tx[u][0] = make_float2(dt * x[u].x, dt * x[u].x);
+                    tx[u][1] = make_float2(dt * x[u].y, dt * x[u].y);
                     y[u][0] = y[u][1] = make_float2(0.0f, 0.0f);
                 }
 #pragma unroll
-                for (int q = 0; q < RQ; q++) {
-                    float4 b[U], c[U];
+                for (int i = 0; i < NI; i++) {
 #pragma unroll
                     for (int u = 0; u < U; u++) {
                         const uint32_t tu = min(tt + u, nt - 1);
-                        b[u] = *reinterpret_cast<const float4*>(Bs + tu * NP + 4 * (s + NS * q));
-                        c[u] = *reinterpret_cast<const float4*>(Cs + tu * NP + 4 * (s + NS * q));
-                    }
+                        const float4 b = *reinterpret_cast<const float4*>(Bs + tu * NP + 4 * (s + NS * i));
+                        const float4 c = *reinterpret_cast<const float4*>(Cs + tu * NP + 4 * (s + NS * i));
+                        const float2 bp[2] = {make_float2(b.x, b.y), make_float2(b.z, b.w)};     // pairs of rows, as they lie in the registers
+                        const float2 cp[2] = {make_float2(c.x, c.y), make_float2(c.z, c.w)};
 #pragma unroll
-                    for (int u = 0; u < U; u++) {          // two columns per instruction: S = dec S + (dt B) x, y += S C
-                        const float bv[4] = {b[u].x * dt[u], b[u].y * dt[u], b[u].z * dt[u], b[u].w * dt[u]};
-                        const float cv[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
-                        const float2 xp[2] = {make_float2(x[u].x, x[u].y), make_float2(x[u].z, x[u].w)};
-                        const float2 d2 = make_float2(dec[u], dec[u]);
-#pragma unroll
-                        for (int r = 0; r < 4; r++) {
-                            const float2 b2 = make_float2(bv[r], bv[r]), c2 = make_float2(cv[r], cv[r]);
+                        for (int k = 0; k < 2; k++)
 #pragma unroll
                             for (int j = 0; j < 2; j++) {
-                                S[q][r][j] = __ffma2_rn(d2, S[q][r][j], __fmul2_rn(b2, xp[j]));
-                                y[u][j] = __ffma2_rn(S[q][r][j], c2, y[u][j]);
+                                S[i][k][j] = __ffma2_rn(d2[u], S[i][k][j], __fmul2_rn(bp[k], tx[u][j]));
+                                y[u][j] = __ffma2_rn(S[i][k][j], cp[k], y[u][j]);
                             }
-                        }
                     }
                 }
 #pragma unroll
                 for (int u = 0; u < U; u++) {
-                    float k;
-                    const float yv[4] = {y[u][0].x, y[u][0].y, y[u][1].x, y[u][1].y};
-                    if (NS >= 4) {                         // scatter: after two steps a lane carries one column, then a plain butterfly
-                        const bool up = (s & (NS / 2)) != 0, up2 = (s & (NS / 4)) != 0;
-                        const float r0 = __shfl_xor_sync(0xffffffffu, up ? yv[0] : yv[2], NS / 2);
-                        const float r1 = __shfl_xor_sync(0xffffffffu, up ? yv[1] : yv[3], NS / 2);
-                        const float k0 = (up ? yv[2] : yv[0]) + r0, k1 = (up ? yv[3] : yv[1]) + r1;
-                        k = (up2 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, up2 ? k0 : k1, NS / 4);
+                    const float y0 = y[u][0].x + y[u][0].y, y1 = y[u][1].x + y[u][1].y;
+                    if (NS >= 2) {
+                        float k = (up ? y1 : y0) + __shfl_xor_sync(0xffffffffu, up ? y0 : y1, NS / 2);
 #pragma unroll
-                        for (uint32_t o = NS / 8; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
-                        const float xs = my_col == 0 ? x[u].x : (my_col == 1 ? x[u].y : (my_col == 2 ? x[u].z : x[u].w));
-                        if (writer && tt + u < nt && p0 + my_col < a.P) a.dst[(size_t)(base + t0 + tt + u) * a.H * a.P + (size_t)h * a.P + p0 + my_col] = fmaf(dsk, xs, k);
-                    } else {
-                        const float xv[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            k = yv[j];
-                            if (NS == 2) k += __shfl_xor_sync(0xffffffffu, k, 1);
-                            if (writer && tt + u < nt && p0 + j < a.P) a.dst[(size_t)(base + t0 + tt + u) * a.H * a.P + (size_t)h * a.P + p0 + j] = fmaf(dsk, xv[j], k);
-                        }
+                        for (uint32_t o = NS / 4; o > 0; o >>= 1) k += __shfl_xor_sync(0xffffffffu, k, o);
+                        const uint32_t col = up ? 1u : 0u;
+                        if (writer && tt + u < nt && p0 + col < a.P) out[(size_t)(tt + u) * a.H * a.P + col] = fmaf(dsk, up ? x[u].y : x[u].x, k);
+                    } else if (tt + u < nt) {
+                        if (p0 < a.P) out[(size_t)(tt + u) * a.H * a.P] = fmaf(dsk, x[u].x, y0);
+                        if (p0 + 1 < a.P) out[(size_t)(tt + u) * a.H * a.P + 1] = fmaf(dsk, x[u].y, y1);
                     }
                 }
             }
         }
     }
 #pragma unroll
-    for (int i = 0; i < 8 * RQ; i++) {
-        st[(2 * i) * kSsmThreads + tid] = S[i / 8][(i / 2) % 4][i % 2].x;
-        st[(2 * i + 1) * kSsmThreads + tid] = S[i / 8][(i / 2) % 4][i % 2].y;
+    for (int i = 0; i < 16 * RQ; i++) {
+        st[(2 * i) * kSsmThreads + tid] = S[i / 4][(i / 2) % 2][i % 2].x;
+        st[(2 * i + 1) * kSsmThreads + tid] = S[i / 4][(i / 2) % 2][i % 2].y;
     }
 }
 static size_t ssm_state_elems(uint32_t H, uint32_t N, uint32_t P) {
-    const uint32_t CPB = kSsmThreads / ssm_slices(N) * 4;
-    return (size_t)H * ((P + CPB - 1) / CPB) * 16 * ssm_rq(N) * kSsmThreads;
+    const uint32_t CPB = kSsmThreads / ssm_slices(N) * 2;
+    return (size_t)H * ((P + CPB - 1) / CPB) * 32 * ssm_rq(N) * kSsmThreads;
 }
 
 // ── MIN_GRU ──────────────────────────────────────────────────────────────────────────────────────────────────────
@@ -428,27 +412,25 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
             a.dst = bufs[s.buf[0]]; a.xbc = bufs[s.buf[1]]; a.dtl = bufs[s.buf[2]]; a.state = bufs[s.buf[4]]; a.ctl = bufs[s.buf[5]];
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.N = s.n[3]; a.P = s.n[4]; a.x_off = s.off[0]; a.b_off = s.off[1]; a.c_off = s.off[2]; a.dt_off = s.off[3];
             a.xbc_rs = s.n[5]; a.dt_rs = s.n[6];
-            const uint32_t NS = ssm_slices(a.N), RQ = ssm_rq(a.N), CPB = kSsmThreads / NS * 4;
+            const uint32_t NS = ssm_slices(a.N), RQ = ssm_rq(a.N), CPB = kSsmThreads / NS * 2;
             // 16-byte copies when every row of B, C and the CTA's x columns starts on a 16-byte boundary
             a.vec = (a.N % 4 == 0 && a.P % 4 == 0 && a.xbc_rs % 4 == 0 && a.x_off % 4 == 0 && a.b_off % 4 == 0 && a.c_off % 4 == 0 &&
                      (reinterpret_cast<uintptr_t>(a.xbc) & 15) == 0) ? 1u : 0u;
             const dim3 grid((a.P + CPB - 1) / CPB, a.H);
-            const size_t smem = ((size_t)2 * kSsmTile * (2 * NS * 4 * RQ + CPB) + 2 * kSsmSpan) * sizeof(float);
+            const size_t smem = ((size_t)2 * kSsmTile * (2 * NS * 16 * RQ + CPB) + 2 * kSsmSpan) * sizeof(float);
 #define ZG_SSM(NS_, RQ_)                                                                                                                  \
     ZG_SEQ_WDT(s.n[7], {                                                                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_, RQ_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
         launch_pdl(k_ssm_scan<WT, NS_, RQ_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
                    wptr<WT>(bufs, s.buf[3], s.off[6]));                                                                                   \
     })
-            if (RQ == 4) ZG_SSM(32, 4);
-            else if (RQ == 2) ZG_SSM(32, 2);
+            if (RQ == 4) ZG_SSM(8, 4);
+            else if (RQ == 2) ZG_SSM(8, 2);
             else switch (NS) {
                 case 1: ZG_SSM(1, 1); break;
                 case 2: ZG_SSM(2, 1); break;
                 case 4: ZG_SSM(4, 1); break;
-                case 8: ZG_SSM(8, 1); break;
-                case 16: ZG_SSM(16, 1); break;
-                default: ZG_SSM(32, 1); break;
+                default: ZG_SSM(8, 1); break;
             }
 #undef ZG_SSM
             ZG_SEQ_CHECK();
