@@ -100,8 +100,8 @@ typedef enum ZgOpTag {
  * EMBED             dst[t, :] = table[ids[t], :] * f0; with n3 = 1 a learned position row joins it, unscaled: + positions[p(t), :]
  *                   (a second table at off 1 of the same arena, p(t) = the token's position in its sequence)
  *                   buf 0 dst 1 ctl 2 table | off 0 table 1 positions | n 0 T 1 D 2 wdt 3 positions | f 0 scale
- * LINEAR            dst[m, n] = sum_k src[m, k] W[n, k] (+ bias[n])
- *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt
+ * LINEAR            dst[m, n] = act(sum_k src[m, k] W[n, k] (+ bias[n])); act (n6): 0 none, 1 + the ACTIVATION kind otherwise
+ *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt 6 act
  * NORM              dst = (res +) norm(src) * w ; kind bit 0 clear: (x - mean) / sqrt(var + eps), set: x / sqrt(mean(x^2) + eps);
  *                   kind bit 1: the weight is stored around zero and applied as (1 + w); kind bit 2: the result is also
  *                   multiplied by the gain f1 (a scale of the following product folded into its input);
@@ -174,8 +174,12 @@ typedef enum ZgOpTag {
  *                   Of the appended columns the first `normed` are RMS-normed with a plain weight (a latent), the next `rot`
  *                   get the token's rotary position (a key part shared by all heads), the rest is copied.  With n9 > 0 the
  *                   normed columns are normed in groups of n9 (key heads), every group with the same weight of n9 values.
- *                   buf 0 cache 1 src 2 ctl 3 norm weight | off 0 src column 1 cache column 2 norm weight
- *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout 9 norm group | f 0 eps 1 rotary base
+ *                   With off5 > 0 the same launch norms off5 QUERY heads of n9 values in place in the source rows (column off 3,
+ *                   weight at off 4), times the temperature 1 + f2 * ln(floor((p + 1) / off6) + 1) (off6 = 0: none): HEAD_NORM fused.
+ *                   buf 0 cache 1 src 2 ctl 3 norm weight | off 0 src column 1 cache column 2 norm weight 3 query column 4 query weight
+ *                   5 query heads 6 temperature period
+ *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout 9 norm group
+ *                   f 0 eps 1 rotary base 2 temperature coefficient
  * CACHED_ATTENTION  softmax attention of the step's queries over cached keys and values.  A query row holds H * maps vectors
  *                   of dk (head h, map m at (h * maps + m) * dk); a key row G * maps vectors of dk; a value row G vectors of
  *                   dv; query (h, m) reads key (h / (H / G), m) and value h / (H / G).  The value cache may be the key cache

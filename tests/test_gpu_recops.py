@@ -236,3 +236,65 @@ def test_malformed_ops_are_refused(cuda_backend):
     ]
     for i, (op, sizes) in enumerate(bad):
         assert cuda_backend.compile_program(DeviceProgram([op], sizes, [], [], [])) is None, i
+
+
+@pytest.mark.parametrize("fmt", ["float32", "bfloat16"])
+def test_linear_activation_epilogue(cuda_backend, fmt):
+    """Every activation in the epilogue of every form of the matmul: one row, a few rows with an odd K, the exact f32 tile and
+    (bfloat16 weights, many rows) the tensor-core product; with and without a bias."""
+    from zgml_b200 import DeviceOp, ExternBuffer, abi
+    from zgml_b200.host.weights import WeightArena
+    wdt = abi.W_F32 if fmt == "float32" else abi.W_BF16
+    r = np.random.default_rng(11)
+
+    def bf16(a):
+        u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+        return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)).view(np.float32)
+
+    for M, N, K in ((1, 24, 64), (3, 17, 37), (40, 70, 50), (70, 96, 128)):
+        W, b = bf16(r.standard_normal((N, K)) / np.sqrt(K)), bf16(0.3 * r.standard_normal(N))
+        x = bf16(r.standard_normal((M, K)) * 1.5)                         # bf16-exact inputs: the tensor-core path rounds nothing away
+        A = WeightArena(wdt)
+        ow, ob = A.add("w", W), A.add("b", b)
+        buf = A.upload(cuda_backend)
+        z = x.astype(np.float64) @ W.astype(np.float64).T
+        for kind in ("relu2", "silu", "gelu_tanh", "relu", None):
+            for bias in (False, True):
+                zz = z + b if bias else z
+                want = {"relu2": np.maximum(zz, 0) ** 2, "silu": zz * sigmoid(zz), "relu": np.maximum(zz, 0), None: zz,
+                        "gelu_tanh": 0.5 * zz * (1 + np.tanh(np.sqrt(2 / np.pi) * (zz + 0.044715 * zz ** 3)))}[kind]
+                op = DeviceOp.linear(0, 1, 2, ow, M, N, K, wdt, bias=2 if bias else None, bias_off=ob, act=kind)
+                got = run(cuda_backend, [op], [M * N, M * K, buf.elems], [(1, x)], 0, (M, N), [ExternBuffer(2, buf)])
+                assert np.abs(got - want).max() < 2e-5 * max(1.0, np.abs(want).max()), (M, N, K, kind, bias)
+        buf.free()
+
+
+def test_cache_append_norms_query_heads(cuda_backend):
+    """The append's second job: query heads normed in place in the source rows, with and without the temperature; the key heads
+    and the copied columns land in the cache as before."""
+    from zgml_b200 import DeviceBuffer, DeviceOp, ExternBuffer, abi
+    r = np.random.default_rng(12)
+    T, H, G, dim, dv, pos, R = 6, 5, 2, 12, 7, 9, 32
+    rs, cw = 3 + H * dim + G * (dim + dv) + 2, G * (dim + dv)
+    x = r.standard_normal((T, rs)).astype(np.float32)
+    wq, wk = (1 + 0.3 * r.standard_normal(dim)).astype(np.float32), (1 + 0.3 * r.standard_normal(dim)).astype(np.float32)
+    w, (oq, ok) = weights(cuda_backend, wq, wk)
+    for coef, every in ((0.0, 0), (0.8, 4)):
+        cache = DeviceBuffer(cuda_backend, 4 * R * cw)
+        op = DeviceOp.cache_append(2, 0, 1, 3 + H * dim, 0, T, cw, rs, cw, R, norm_w=3, norm_off=ok, normed=G * dim, eps=1e-5, wdt=abi.W_F32, norm_group=dim,
+                                   q_heads=H, q_col=3, q_norm_off=oq, temp_coef=coef, temp_every=every)
+        got = run(cuda_backend, [op], [x.size, 8, cache.elems, w.elems], [(0, x), (1, ctl_words(pos, 0))], 0, x.shape, [ExternBuffer(2, cache), ExternBuffer(3, w)])
+        rows = cache.download(np.float32, 4 * pos * cw, T * cw).reshape(T, cw)
+        want = x.astype(np.float64).copy()
+        for t in range(T):
+            temp = 1.0 + coef * np.log((pos + t + 1) // every + 1) if every else 1.0
+            q = want[t, 3:3 + H * dim].reshape(H, dim)
+            q /= np.sqrt((q ** 2).mean(-1, keepdims=True) + 1e-5)
+            q *= wq * temp
+        assert np.abs(got - want).max() < 1e-5                              # the queries changed, nothing else of the rows did
+        k = x[:, 3 + H * dim:3 + H * dim + G * dim].astype(np.float64).reshape(T, G, dim)
+        k = k / np.sqrt((k ** 2).mean(-1, keepdims=True) + 1e-5) * wk
+        assert np.abs(rows[:, :G * dim] - k.reshape(T, -1)).max() < 1e-5
+        assert np.array_equal(rows[:, G * dim:], x[:, 3 + H * dim + G * dim:3 + H * dim + cw])
+        cache.free()
+    w.free()

@@ -82,8 +82,9 @@ def test_state_and_lowering_shape(fake_device):
         tags = [op.tag for op in ops]
         assert tags[0] == abi.OP_EMBED and ops[0].u.seq.n[3] == 1 and lp.logits_rows == rows and (lp.buf_logits is None) == (head == "none")
         assert tags.count(abi.OP_SSM_SCAN) == 2 and tags.count(abi.OP_CAUSAL_CONV) == 2 and tags.count(abi.OP_GATED_NORM) == 2
-        assert tags.count(abi.OP_CACHED_ATTENTION) == 3 and tags.count(abi.OP_CACHE_APPEND) == 3 and tags.count(abi.OP_HEAD_NORM) == 3 and tags.count(abi.OP_MIN_GRU) == 3
-        assert tags.count(abi.OP_ACTIVATION) == 2 and tags.count(abi.OP_MOE_FFN) == 2 and tags.count(abi.OP_ROUTE) == 2
+        assert tags.count(abi.OP_CACHED_ATTENTION) == 3 and tags.count(abi.OP_CACHE_APPEND) == 3 and tags.count(abi.OP_HEAD_NORM) == 0 and tags.count(abi.OP_MIN_GRU) == 3
+        assert tags.count(abi.OP_ACTIVATION) == 0 and sum(op.tag == abi.OP_LINEAR and op.u.seq.n[6] == 1 for op in ops) == 2     # relu^2 rides in the up projection
+        assert tags.count(abi.OP_MOE_FFN) == 2 and tags.count(abi.OP_ROUTE) == 2
         att = [op for op in ops if op.tag == abi.OP_CACHED_ATTENTION]
         assert all(op.u.seq.off[5] == abi.WEIGHTS_SIGMOID and op.u.seq.buf[5] != abi.NO_BUF and op.u.seq.off[6] == 100 for op in att)
         assert att[0].u.seq.buf[5] == att[1].u.seq.buf[5] != att[2].u.seq.buf[5]      # one distance table per set of weights

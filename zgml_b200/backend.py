@@ -212,9 +212,10 @@ class DeviceOp:
         return DeviceOp._seq(abi.OP_EMBED, [dst, ctl, table], [table_off, positions_off or 0], [T, D, wdt, int(positions_off is not None)], [scale])
 
     @staticmethod
-    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0):
+    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0, act=None):
+        """`act`: an activation of abi.ACTIVATIONS applied in the epilogue, after the bias."""
         return DeviceOp._seq(abi.OP_LINEAR, [dst, src, w, bias], [w_off, bias_off, src_off, dst_off],
-                             [M, N, K, src_rs or K, dst_rs or N, wdt])
+                             [M, N, K, src_rs or K, dst_rs or N, wdt, 0 if act is None else abi.ACTIVATIONS[act] + 1])
 
     @staticmethod
     def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer",
@@ -300,10 +301,12 @@ class DeviceOp:
 
     @staticmethod
     def cache_append(cache, src, ctl, src_col, cache_col, T, cols, src_rs, width, rows, norm_w=None, norm_off=0, normed=0, eps=0.0, wdt=0,
-                     rot=0, rot_base=0.0, rot_layout="pairs", norm_group=0):
-        """`norm_group` > 0: the normed columns are normed in groups of that many (key heads) sharing one weight of that size."""
-        return DeviceOp._seq(abi.OP_CACHE_APPEND, [cache, src, ctl, norm_w if normed else None], [src_col, cache_col, norm_off],
-                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout], norm_group], [eps, rot_base])
+                     rot=0, rot_base=0.0, rot_layout="pairs", norm_group=0, q_heads=0, q_col=0, q_norm_off=0, temp_coef=0.0, temp_every=0):
+        """`norm_group` > 0: the normed columns are normed in groups of that many (key heads) sharing one weight of that size.
+        `q_heads` > 0: that many query heads of norm_group values at column q_col of the source rows are normed in place by the same
+        launch (weight at q_norm_off of norm_w's arena), times the position-dependent temperature of HEAD_NORM."""
+        return DeviceOp._seq(abi.OP_CACHE_APPEND, [cache, src, ctl, norm_w if normed else None], [src_col, cache_col, norm_off, q_col, q_norm_off, q_heads, temp_every],
+                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout], norm_group], [eps, rot_base, temp_coef])
 
     @staticmethod
     def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,

@@ -67,7 +67,7 @@ __global__ void k_rotary(float* x, const float* src, const float* __restrict__ c
 template <typename WT>
 __global__ void k_cache_append(float* __restrict__ cache, const float* __restrict__ src, const float* __restrict__ ctl, const WT* __restrict__ nw_,
                                uint32_t cols, uint32_t src_rs, uint32_t width, uint32_t R, uint32_t normed, uint32_t rot, uint32_t layout, float eps,
-                               float base, uint32_t norm_group) {
+                               float base, uint32_t norm_group, float* qsrc, const WT* __restrict__ qw, uint32_t q_heads, uint32_t temp_every, float temp_coef) {
     pdl_enter();
     __shared__ float sh[32];
     const uint32_t t = blockIdx.x;
@@ -98,6 +98,18 @@ __global__ void k_cache_append(float* __restrict__ cache, const float* __restric
         row[b] = w * cs + u * sn;
     }
     for (uint32_t c = normed + rot + threadIdx.x; c < cols; c += blockDim.x) row[c] = s[c];
+    if (q_heads) {     // the step's QUERY heads are normed in place by the same launch (per head, one shared weight), times a temperature that grows with the position
+        const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        const float temp = temp_every ? fmaf(temp_coef, logf((float)((pos + 1) / temp_every) + 1.0f), 1.0f) : 1.0f;
+        float* qrow = qsrc + (size_t)t * src_rs;
+        for (uint32_t hd = warp; hd < q_heads; hd += nw) {
+            float* v = qrow + (size_t)hd * norm_group;
+            float q = 0.0f;
+            for (uint32_t c = lane; c < norm_group; c += 32) q = fmaf(v[c], v[c], q);
+            const float mult = temp / sqrtf(warp_sum(q) / (float)norm_group + eps);
+            for (uint32_t c = lane; c < norm_group; c += 32) v[c] = v[c] * wld(qw, c) * mult;
+        }
+    }
 }
 
 // ── CACHED_ATTENTION ─────────────────────────────────────────────────────────────────────────────────────────────
@@ -787,6 +799,11 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (normed && s.n[9] && normed % s.n[9]) return fail("cache_append: norm groups");
             if (normed && !wfits(3, s.n[7], s.off[2], s.n[9] ? s.n[9] : normed)) return fail("cache_append: norm weight");
             if (rot && !(s.f[1] > 0.0f)) return fail("cache_append: rotary base");
+            if (s.off[5]) {    // query heads normed in place in the source rows
+                const size_t qh = s.off[5], hd = s.n[9];
+                if (!normed || !hd || s.off[3] + qh * hd > srs || !fits(1, 0, (T - 1) * srs + s.off[3] + qh * hd) || !wfits(3, s.n[7], s.off[4], hd)) return fail("cache_append: query heads");
+                if (s.off[3] < s.off[0] + cols && s.off[0] < s.off[3] + qh * hd) return fail("cache_append: query heads overlap the appended columns");
+            }
             return true;
         }
         case ZG_OP_CACHED_ATTENTION: {
@@ -841,6 +858,7 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
 }
 
 uint32_t zg_mix_op_writes(uint32_t tag) {
+    if (tag == ZG_OP_CACHE_APPEND) return 1u | (1u << 1);   // the source rows too: query heads may be normed in place
     return tag == ZG_OP_TOKEN_SHIFT ? (1u | (1u << 3)) : 1u;
 }
 
@@ -877,7 +895,8 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
         }
         case ZG_OP_CACHE_APPEND:
             ZG_SEQ_WDT(s.n[5] ? s.n[7] : ZG_W_F32, launch_pdl(k_cache_append<WT>, dim3(s.n[0]), dim3(128), 0, st, bufs[s.buf[0]] + s.off[1], bufs[s.buf[1]] + s.off[0], bufs[s.buf[2]],
-                                                             s.n[5] ? wptr<WT>(bufs, s.buf[3], s.off[2]) : nullptr, s.n[1], s.n[2], s.n[3], s.n[4], s.n[5], s.n[6], s.n[8], s.f[0], s.f[1], s.n[9]));
+                                                             s.n[5] ? wptr<WT>(bufs, s.buf[3], s.off[2]) : nullptr, s.n[1], s.n[2], s.n[3], s.n[4], s.n[5], s.n[6], s.n[8], s.f[0], s.f[1], s.n[9],
+                                                             s.off[5] ? bufs[s.buf[1]] + s.off[3] : nullptr, s.off[5] ? wptr<WT>(bufs, s.buf[3], s.off[4]) : nullptr, s.off[5], s.off[6], s.f[2]));
             ZG_SEQ_CHECK();
             return true;
         case ZG_OP_CACHED_ATTENTION: {

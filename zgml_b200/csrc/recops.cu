@@ -325,14 +325,6 @@ __global__ void k_head_norm(float* x, const WT* __restrict__ w, const float* __r
 }
 
 // ── ACTIVATION ───────────────────────────────────────────────────────────────────────────────────────────────────
-__device__ __forceinline__ float activation(float z, uint32_t kind) {
-    switch (kind) {
-        case 0: { const float r = fmaxf(z, 0.0f); return r * r; }
-        case 1: return z * sigmoidf_(z);
-        case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
-        default: return fmaxf(z, 0.0f);
-    }
-}
 // four elements per thread (n a multiple of 4, both buffers on 16-byte boundaries) or one
 template <bool VEC>
 __global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t kind) {
@@ -341,11 +333,11 @@ __global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t 
     if (VEC) {
         if (4 * e >= n) return;
         float4 v = reinterpret_cast<const float4*>(src)[e];
-        v.x = activation(v.x, kind); v.y = activation(v.y, kind); v.z = activation(v.z, kind); v.w = activation(v.w, kind);
+        v.x = seq_activation(v.x, kind); v.y = seq_activation(v.y, kind); v.z = seq_activation(v.z, kind); v.w = seq_activation(v.w, kind);
         reinterpret_cast<float4*>(dst)[e] = v;
     } else {
         if (e >= n) return;
-        dst[e] = activation(src[e], kind);
+        dst[e] = seq_activation(src[e], kind);
     }
 }
 

@@ -32,7 +32,7 @@ __global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, 
 constexpr int kGemvRows = 8;
 template <typename WT>
 __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
-                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
+                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
     pdl_enter();
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (n >= N) return;
@@ -51,7 +51,7 @@ __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__
     for (int m = 0; m < kGemvRows; m++) {
         if (m < (int)M) {
             const float s = warp_sum(acc[m]);
-            if (lane == 0) dst[(size_t)m * dst_rs + n] = s + b;
+            if (lane == 0) dst[(size_t)m * dst_rs + n] = seq_epilogue(s + b, act);
         }
     }
 }
@@ -59,7 +59,7 @@ __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__
 // vectors per lane are in flight per trip.
 template <typename WT, int MR>
 __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
-                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs) {
+                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
     // Weights are constants of the model, so this warp's weight row is pulled toward L2 BEFORE the wait on the predecessor:
     // in a replayed graph the HBM stream of a matvec starts under the tail of the kernel that produces its input.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -124,7 +124,7 @@ __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restri
     for (int m = 0; m < MR; m++) {
         if (m < (int)M) {
             const float s = warp_sum(acc[m]);
-            if (lane == 0) dst[(size_t)m * dst_rs + n] = s + b;
+            if (lane == 0) dst[(size_t)m * dst_rs + n] = seq_epilogue(s + b, act);
         }
     }
 }
@@ -134,7 +134,7 @@ constexpr int kTM = 64, kTN = 64, kTK = 16;
 template <typename WT>
 __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W,
                                                      const WT* __restrict__ bias, uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs,
-                                                     uint32_t dst_rs) {
+                                                     uint32_t dst_rs, uint32_t act) {
     __shared__ float As[kTK][kTM + 4];
     __shared__ float Ws[kTK][kTN + 4];
     const uint32_t m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, co
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint32_t n = n0 + tx * 4 + j;
-            if (n < N) dst[(size_t)m * dst_rs + n] = acc[i][j] + (bias ? wld(bias, n) : 0.0f);
+            if (n < N) dst[(size_t)m * dst_rs + n] = seq_epilogue(acc[i][j] + (bias ? wld(bias, n) : 0.0f), act);
         }
     }
 }
@@ -1418,6 +1418,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!fits(0, s.off[3], (M - 1) * drs + N) || !fits(1, s.off[2], (M - 1) * srs + K) || !wfits(2, s.off[0], N * K)) return fail("linear: extent");
             if (s.buf[3] != ZG_NO_BUF && !wfits(3, s.off[1], N)) return fail("linear: bias extent");
             if (s.buf[0] == s.buf[1]) return fail("linear: in place");
+            if (s.n[6] > 4) return fail("linear: activation");
             return true;
         }
         case ZG_OP_NORM: {
@@ -1547,7 +1548,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const bool has_bias = s.buf[3] != ZG_NO_BUF;
             if (scratch && zg_seq_op_scratch_elems(op, bufs))
                 return zg_dense_gemm_launch(wptr<bf16>(bufs, s.buf[2], s.off[0]), has_bias ? wptr<bf16>(bufs, s.buf[3], s.off[1]) : nullptr, src, dst, M, N, K,
-                                            s.n[3], s.n[4], scratch, st);
+                                            s.n[3], s.n[4], scratch, st, s.n[6]);
             ZG_SEQ_WDT(s.n[5], {
                 const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
                 const WT* b = has_bias ? wptr<WT>(bufs, s.buf[3], s.off[1]) : nullptr;
@@ -1556,13 +1557,13 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                     const size_t xs_bytes = (size_t)M * K * sizeof(float);
                     const bool vec = K % V == 0 && (reinterpret_cast<size_t>(W) & 15) == 0 && xs_bytes <= 48 * 1024;
                     const dim3 grid((N + 7) / 8);
-                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
-                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
-                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
-                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
+                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
+                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
+                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
                 } else {
                     const dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
-                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4]);
+                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
                 }
             });
             ZG_SEQ_CHECK();

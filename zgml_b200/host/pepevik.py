@@ -15,12 +15,12 @@ Per layer (x: f32 stream, m: the residual multiplier):   x += m mixer(DyT(x; nor
 
 mamba2      [z | x | B | C | dt] = W_in h in ONE matmul; CAUSAL_CONV (bias, SiLU) over x | B | C; SSM_SCAN; GATED_NORM
             (y silu(z), RMS norm in equal parts, weight); W_o.
-parallel    [q | k | v | z | u | g] = W h + b in ONE matmul for both branches.  Left: HEAD_NORM on the queries (with the
-            temperature), CACHE_APPEND norms the key heads on their way into the cache, CACHED_ATTENTION with sigmoid weights;
+parallel    [q | k | v | z | u | g] = W h + b in ONE matmul for both branches.  Left: CACHE_APPEND norms the key heads on
+            their way into the cache and the query heads (with the temperature) in place, CACHED_ATTENTION with sigmoid weights;
             the distance penalty and the per-head score bias are ONE table per layer, pb_h - r1_h ln(1 + r2_h d), evaluated in
             f32 at load for every distance the cache can hold.  Right: MIN_GRU.  Each branch has its own W_o; the two RMS
             norms of the results and their sum are one residual step with two sources.
-feed-forward dense: W_up, ACTIVATION relu^2, W_down.  moe: router matmul, ROUTE "corrected_sigmoid" with groups, MOE_FFN.
+feed-forward dense: W_up with relu^2 in its epilogue, W_down.  moe: router matmul, ROUTE "corrected_sigmoid" with groups, MOE_FFN.
 """
 import json
 import os
@@ -354,9 +354,10 @@ class PepevikModel:
                 cache = pool.buffers[f"l{i}.kv"]
                 cw = G * (dim + vdim)
                 R = cache.elems // (slots * cw)
-                ops.append(DeviceOp.head_norm(proj, wb, A.off["q.norm"], ctl, 0, T, H, dim, ni, eps, wdt, temp_coef=l["q_temp"]["coef"], temp_every=l["q_temp"]["every"]))
+                # one launch norms the key heads on their way into the cache and the query heads (with the temperature) in place
                 ops.append(DeviceOp.cache_append(ext(cache), proj, ctl, meta["k_col"], 0, T, cw, ni, cw, R, norm_w=wb, norm_off=A.off["k.norm"], normed=G * dim,
-                                                 eps=eps, wdt=wdt, norm_group=dim))
+                                                 eps=eps, wdt=wdt, norm_group=dim, q_heads=H, q_col=0, q_norm_off=A.off["q.norm"], temp_coef=l["q_temp"]["coef"],
+                                                 temp_every=l["q_temp"]["every"]))
                 att = scratch("att", T * H * vdim)
                 ops.append(DeviceOp.cached_attention(att, proj, ext(cache), ext(cache), ctl, 0, 0, G * dim, T, H, G, 1, dim, vdim, ni, cw, cw, R, l["scale"],
                                                      weights="sigmoid", score_table=ext(self._score_table(owner, R)), table_len=R))
@@ -373,8 +374,7 @@ class PepevikModel:
                 if mlp["kind"] == "dense":
                     ff = meta["ff"]
                     u = scratch("ff", T * ff)
-                    ops.append(DeviceOp.linear(u, h, wb, A.off["up"], T, ff, D, wdt))
-                    ops.append(DeviceOp.activation(u, u, T * ff, "relu2"))
+                    ops.append(DeviceOp.linear(u, h, wb, A.off["up"], T, ff, D, wdt, act="relu2"))      # the squared ReLU rides in the epilogue
                     ops.append(DeviceOp.linear(y, u, wb, A.off["down"], T, D, ff, wdt))
                 else:
                     E, ff, top = meta["E"], meta["ff"], meta["top"]
