@@ -323,6 +323,27 @@ def test_long_cache_and_split_decoding(cuda_backend, layer):
     close(s)
 
 
+def test_long_steps_walk_segments_side_by_side(cuda_backend):
+    """Steps of 256 tokens: the state-space scan cuts them into segments walked side by side (each first from an empty state, then
+    from the state the fold gives it) and the recurrent unit into 64; the states they leave must carry on into smaller steps and
+    single tokens, in a slot that is not the first, after a request that used the same slot before."""
+    cfg = config([ssm_layer(heads=4, vdim=8, state=24, groups=2, conv=4, norm_groups=2, mlp=dense()), ssm_layer(heads=2, vdim=12, state=200, groups=1, conv=2, norm_groups=3),
+                  pair_layer(heads=2, kv_heads=1, dim=8, vdim=8, gru=70, every=100, mlp=moe()), ssm_layer(heads=4, vdim=8, state=24, groups=2, conv=4, norm_groups=2, weights_of=0, mlp=dense())],
+                 width=48, vocab=50, max_positions=700)
+    W = random_weights(cfg, seed=23, qk_gain=2.0)
+    n = 600
+    toks = tokens(cfg, n)
+    want, _ = ref.forward(cfg, as_f64(W), toks)
+    s = open_model(cuda_backend, cfg, W, "float32", n_slots=2, max_chunk=256, max_context=640)
+    s.feed("first", toks[:5], [])                           # takes slot 0 and keeps it
+    s.feed("other", toks[100:400], [])                      # leaves its states in slot 1
+    s.release("other")
+    got = np.concatenate([s.feed("a", toks[:570], range(570))] + [s.feed("a", [t], [0]) for t in toks[570:]])   # 256 + 256 + 32 + 16 + 8 + 2, then single tokens
+    assert s.pool.slot("a") == 1
+    assert rel(got, want) < TOL
+    close(s)
+
+
 def test_long_decoding(cuda_backend):
     """150 decoded tokens through every kind of state: the recurrent states, the convolution inputs and a growing cache."""
     cfg = config([ssm_layer(mlp=moe()), pair_layer(mlp=dense(), every=16), ssm_layer(weights_of=0, mlp=moe()), pair_layer(weights_of=1, mlp=dense(), every=16)])

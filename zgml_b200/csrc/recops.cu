@@ -29,7 +29,8 @@ constexpr int kLongWalk = 64;
 // after the first step a lane carries one of the two columns.
 // Step sizes and decays of the head (softplus, two exponentials) are evaluated for a span of tokens at once, in parallel,
 // before the walk; B, C and the CTA's x columns arrive in tiles of kSsmTile tokens through cp.async, two tiles in flight, so
-// the next tile's loads run under this tile's walk; two tokens are walked per trip so that their loads and sums interleave.
+// the next tile's loads run under this tile's walk; four tokens are walked per trip so that their loads and sums interleave.
+// A step of many tokens in a model with few (head, column block) pairs is cut into segments walked side by side (SsmArgs::mode).
 // State in memory: [H][column blocks][32 RQ][kSsmThreads], element (i, thread) — each thread's block, fully coalesced; the
 // layout is private to the op (zeros mean an empty state in any layout).
 constexpr int kSsmThreads = 128, kSsmTile = 16, kSsmSpan = 1024, kSsmMaxN = 512;
@@ -42,6 +43,13 @@ __host__ __device__ inline uint32_t ssm_slices(uint32_t N) {
 struct SsmArgs {
     float* dst; const float* xbc; const float* dtl; float* state; const float* ctl;
     uint32_t T, H, G, N, P, x_off, b_off, c_off, dt_off, xbc_rs, dt_rs, vec;
+    // Segments of a long step walked side by side (the recurrence is linear in the state).  mode 0: the whole step from the carried
+    // state.  mode 1: segment blockIdx.z from an EMPTY state, no read-out; leaves the state it reaches and the product of its decays.
+    // mode 2: segment blockIdx.z from the state it really starts from (segment 0: the carried one), with the read-out; the last
+    // segment leaves the carried state.  Between the two, k_ssm_fold turns the reached states into starting states.
+    uint32_t mode, seg_len;
+    float* seg_state;      // [segments - 1][state elements of one slot]
+    float* seg_decay;      // [segments - 1][H]
 };
 // global -> shared without passing through registers, 4 or 16 bytes; `on` false writes zeros (nothing is read)
 __device__ __forceinline__ void ssm_copy4(float* dst, const float* src, bool on) {
@@ -67,13 +75,19 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
     const uint32_t p0 = cb * CPB + pl * 2;                               // this thread's first column
     const uint32_t slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
     const uint32_t n_cb = (a.P + CPB - 1) / CPB;
-    float* st = a.state + (((size_t)slot * a.H + h) * n_cb + cb) * (32 * RQ * kSsmThreads);
+    constexpr size_t kBlock = (size_t)32 * RQ * kSsmThreads;             // state elements of one (head, column block)
+    const size_t slot_elems = (size_t)a.H * n_cb * kBlock, my_block = ((size_t)h * n_cb + cb) * kBlock;
+    float* st = a.state + slot * slot_elems + my_block;
+    const uint32_t seg = a.mode ? blockIdx.z : 0, n_seg = a.mode ? (a.T + a.seg_len - 1) / a.seg_len : 1;
+    const uint32_t t_begin = a.mode ? seg * a.seg_len : 0, t_end = a.mode ? min(a.T, t_begin + a.seg_len) : a.T;
+    const float* from = a.mode == 2 && seg > 0 ? a.seg_state + (size_t)(seg - 1) * slot_elems + my_block : st;
     float2 S[NI][2][2];                                                  // [float4 of rows][pair of rows in it][column]
 #pragma unroll
     for (int i = 0; i < 16 * RQ; i++) {
-        S[i / 4][(i / 2) % 2][i % 2].x = st[(2 * i) * kSsmThreads + tid];
-        S[i / 4][(i / 2) % 2][i % 2].y = st[(2 * i + 1) * kSsmThreads + tid];
+        S[i / 4][(i / 2) % 2][i % 2].x = a.mode == 1 ? 0.0f : from[(2 * i) * kSsmThreads + tid];
+        S[i / 4][(i / 2) % 2][i % 2].y = a.mode == 1 ? 0.0f : from[(2 * i + 1) * kSsmThreads + tid];
     }
+    float decay_product = 1.0f;                                          // mode 1, thread 0
     const float neg_a = -expf(wld(a_log, h)), bias = wld(dt_bias, h), dsk = wld(dskip, h);
     const float* bsrc = a.xbc + a.b_off + (size_t)g * a.N;
     const float* csrc = a.xbc + a.c_off + (size_t)g * a.N;
@@ -87,7 +101,7 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
         float* Bs = sm + stage * kStage;
         float* Cs = Bs + kSsmTile * NP;
         float* Xs = Cs + kSsmTile * NP;
-        const uint32_t nt = min((uint32_t)kSsmTile, a.T - t0);
+        const uint32_t nt = min((uint32_t)kSsmTile, t_end - t0);
         if (a.vec) {
             for (uint32_t e = tid; e < nt * (NP / 4); e += kSsmThreads) {
                 const uint32_t tt = e / (NP / 4), n = 4 * (e % (NP / 4));
@@ -114,8 +128,8 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
             ssm_copy4(Xs + e, on ? xsrc + (size_t)(t0 + tt) * a.xbc_rs + c : a.xbc, on);
         }
     };
-    for (uint32_t base = 0; base < a.T; base += kSsmSpan) {
-        const uint32_t span = min((uint32_t)kSsmSpan, a.T - base);
+    for (uint32_t base = t_begin; base < t_end; base += kSsmSpan) {
+        const uint32_t span = min((uint32_t)kSsmSpan, t_end - base);
         __syncthreads();                                   // the previous span's readers are done
         fetch_tile(base, 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -128,13 +142,15 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
             const uint32_t stage = it & 1;
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();                               // tile `it` has landed for everyone, and everyone has left tile it - 1
+            if (a.mode == 1 && tid == 0)
+                for (uint32_t t = t0; t < min(span, t0 + kSsmTile); t++) decay_product *= Dec[t];
             if (t0 + kSsmTile < span) fetch_tile(base + t0 + kSsmTile, stage ^ 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
             const float* Bs = sm + stage * kStage;
             const float* Cs = Bs + kSsmTile * NP;
             const float* Xs = Cs + kSsmTile * NP;
             const uint32_t nt = min((uint32_t)kSsmTile, span - t0);
-            constexpr int U = 2;                           // tokens per trip
+            constexpr int U = RQ > 1 ? 2 : 4;              // tokens per trip (4: 238 us per 1024-token walk at 64 heads, 2: 252, 1: 267)
             float* out = a.dst + (size_t)(base + t0) * a.H * a.P + (size_t)h * a.P + p0;
             for (uint32_t tt = 0; tt < nt; tt += U) {
                 float2 x[U], d2[U], tx[U][2], y[U][2];
@@ -167,6 +183,7 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
                             }
                     }
                 }
+                if (a.mode == 1) continue;                 // no read-out on the walk from an empty state
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     const float y0 = y[u][0].x + y[u][0].y, y1 = y[u][1].x + y[u][1].y;
@@ -185,15 +202,47 @@ __global__ void __launch_bounds__(kSsmThreads) k_ssm_scan(SsmArgs a, const WT* _
         }
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (a.mode == 2 && seg + 1 < n_seg) return;            // only the last segment leaves the carried state
+    float* to = a.mode == 1 ? a.seg_state + (size_t)seg * slot_elems + my_block : st;
 #pragma unroll
     for (int i = 0; i < 16 * RQ; i++) {
-        st[(2 * i) * kSsmThreads + tid] = S[i / 4][(i / 2) % 2][i % 2].x;
-        st[(2 * i + 1) * kSsmThreads + tid] = S[i / 4][(i / 2) % 2][i % 2].y;
+        to[(2 * i) * kSsmThreads + tid] = S[i / 4][(i / 2) % 2][i % 2].x;
+        to[(2 * i + 1) * kSsmThreads + tid] = S[i / 4][(i / 2) % 2][i % 2].y;
+    }
+    if (a.mode == 1 && cb == 0 && tid == 0) a.seg_decay[(size_t)seg * a.H + h] = decay_product;
+}
+// Starting states of the segments: start[0] is the carried state, start[j] = (product of segment j - 1's decays) start[j - 1] + the
+// state segment j - 1 reached from empty.  start[j] replaces reached[j - 1] in place; one thread per state element.
+__global__ void k_ssm_fold(float* __restrict__ seg_state, const float* __restrict__ seg_decay, const float* __restrict__ state, const float* __restrict__ ctl,
+                           uint32_t H, uint32_t head_elems, uint32_t n_seg) {
+    pdl_enter();
+    const size_t slot_elems = (size_t)H * head_elems, e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= slot_elems) return;
+    const uint32_t h = (uint32_t)(e / head_elems);
+    float s = state[(size_t)ctl_word(ctl, ZG_CTL_SLOT) * slot_elems + e];
+    for (uint32_t j = 0; j + 1 < n_seg; j++) {
+        s = fmaf(seg_decay[(size_t)j * H + h], s, seg_state[(size_t)j * slot_elems + e]);
+        seg_state[(size_t)j * slot_elems + e] = s;
     }
 }
 static size_t ssm_state_elems(uint32_t H, uint32_t N, uint32_t P) {
     const uint32_t CPB = kSsmThreads / ssm_slices(N) * 2;
     return (size_t)H * ((P + CPB - 1) / CPB) * 32 * ssm_rq(N) * kSsmThreads;
+}
+// Segments a step is cut into: a walk is bound by the dependent issue of its warps (a warp uses about a quarter of its scheduler's
+// issue slots), one CTA per (head, column block), so a long step of a model with few of those is cut while the GPU still holds
+// no more than about three CTAs per SM — beyond that the second walk of every token costs more than the segments gain
+// (measured at 1024 tokens: 32 heads 252 -> 115 us, 64 heads 252 -> 211 us with five segments, 128 heads 308 -> 373 us with
+// three).  A segment has at least 64 tokens.
+static uint32_t ssm_segments(uint32_t T, uint32_t H, uint32_t N, uint32_t P, uint32_t* seg_len) {
+    const uint32_t CPB = kSsmThreads / ssm_slices(N) * 2, ctas = H * ((P + CPB - 1) / CPB);
+    uint32_t n = 448 / (ctas ? ctas : 1);
+    if (n > 8) n = 8;
+    if (n > T / 64) n = T / 64;
+    if (n < 2) { *seg_len = T; return 1; }
+    const uint32_t len = ((T + n - 1) / n + kSsmTile - 1) / kSsmTile * kSsmTile;
+    *seg_len = len;
+    return (T + len - 1) / len;
 }
 
 // ── MIN_GRU ──────────────────────────────────────────────────────────────────────────────────────────────────────
@@ -343,6 +392,16 @@ __global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t 
 
 }  // namespace
 
+// shared scratch of a long SSM_SCAN step: per segment but the last, a state (reached, then starting) and the product of its decays per head
+size_t zg_rec_op_scratch_elems(const ZgOp& op) {
+    if (op.tag != ZG_OP_SSM_SCAN) return 0;
+    const ZgSeqOp& s = op.u.seq;
+    if (!s.n[1] || !s.n[3] || !s.n[4] || s.n[3] > (uint32_t)kSsmMaxN) return 0;
+    uint32_t len;
+    const uint32_t n = ssm_segments(s.n[0], s.n[1], s.n[3], s.n[4], &len);
+    return n > 1 ? (size_t)(n - 1) * (ssm_state_elems(s.n[1], s.n[3], s.n[4]) + s.n[1]) : 0;
+}
+
 // f32 slots per state slot of an op whose state layout is its own (SSM_SCAN); 0 for every other op
 extern "C" __attribute__((visibility("default"))) size_t zg_cuda_seq_state_elems(const ZgOp* op) {
     if (!op || op->tag != ZG_OP_SSM_SCAN) return 0;
@@ -405,7 +464,7 @@ uint32_t zg_rec_op_writes(uint32_t tag) {
     }
 }
 
-bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
+bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st) {
     const ZgSeqOp& s = op.u.seq;
     switch (op.tag) {
         case ZG_OP_SSM_SCAN: {
@@ -417,22 +476,45 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, cudaStream_t st) {
             // 16-byte copies when every row of B, C and the CTA's x columns starts on a 16-byte boundary
             a.vec = (a.N % 4 == 0 && a.P % 4 == 0 && a.xbc_rs % 4 == 0 && a.x_off % 4 == 0 && a.b_off % 4 == 0 && a.c_off % 4 == 0 &&
                      (reinterpret_cast<uintptr_t>(a.xbc) & 15) == 0) ? 1u : 0u;
-            const dim3 grid((a.P + CPB - 1) / CPB, a.H);
             const size_t smem = ((size_t)2 * kSsmTile * (2 * NS * 16 * RQ + CPB) + 2 * kSsmSpan) * sizeof(float);
+            const size_t slot_elems = ssm_state_elems(a.H, a.N, a.P);
+            uint32_t seg_len = a.T;
+            const uint32_t n_seg = scratch ? ssm_segments(a.T, a.H, a.N, a.P, &seg_len) : 1;
+            a.seg_len = seg_len;
+            a.seg_state = scratch;
+            a.seg_decay = scratch ? scratch + (size_t)(n_seg > 1 ? n_seg - 1 : 0) * slot_elems : nullptr;
 #define ZG_SSM(NS_, RQ_)                                                                                                                  \
     ZG_SEQ_WDT(s.n[7], {                                                                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_ssm_scan<WT, NS_, RQ_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-        launch_pdl_if(a.T < (uint32_t)kLongWalk, k_ssm_scan<WT, NS_, RQ_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), wptr<WT>(bufs, s.buf[3], s.off[5]), \
-                   wptr<WT>(bufs, s.buf[3], s.off[6]));                                                                                   \
+        launch_pdl_if(a.T < (uint32_t)kLongWalk, k_ssm_scan<WT, NS_, RQ_>, grid, dim3(kSsmThreads), smem, st, a, wptr<WT>(bufs, s.buf[3], s.off[4]), \
+                      wptr<WT>(bufs, s.buf[3], s.off[5]), wptr<WT>(bufs, s.buf[3], s.off[6]));                                            \
     })
-            if (RQ == 4) ZG_SSM(8, 4);
-            else if (RQ == 2) ZG_SSM(8, 2);
-            else switch (NS) {
-                case 1: ZG_SSM(1, 1); break;
-                case 2: ZG_SSM(2, 1); break;
-                case 4: ZG_SSM(4, 1); break;
-                default: ZG_SSM(8, 1); break;
+#define ZG_SSM_ANY()                                                                                                                      \
+    do {                                                                                                                                  \
+        if (RQ == 4) ZG_SSM(8, 4);                                                                                                        \
+        else if (RQ == 2) ZG_SSM(8, 2);                                                                                                   \
+        else switch (NS) {                                                                                                                \
+            case 1: ZG_SSM(1, 1); break;                                                                                                  \
+            case 2: ZG_SSM(2, 1); break;                                                                                                  \
+            case 4: ZG_SSM(4, 1); break;                                                                                                  \
+            default: ZG_SSM(8, 1); break;                                                                                                 \
+        }                                                                                                                                 \
+    } while (0)
+            dim3 grid((a.P + CPB - 1) / CPB, a.H, 1);
+            if (n_seg > 1) {       // every segment but the last from an empty state, the fold, then every segment from its real start
+                a.mode = 1; grid.z = n_seg - 1;
+                ZG_SSM_ANY();
+                ZG_SEQ_CHECK();
+                launch_pdl(k_ssm_fold, dim3((unsigned)((slot_elems + 255) / 256)), dim3(256), 0, st, a.seg_state, (const float*)a.seg_decay, (const float*)a.state, a.ctl, a.H,
+                           (uint32_t)(slot_elems / a.H), n_seg);
+                ZG_SEQ_CHECK();
+                a.mode = 2; grid.z = n_seg;
+                ZG_SSM_ANY();
+            } else {
+                a.mode = 0;
+                ZG_SSM_ANY();
             }
+#undef ZG_SSM_ANY
 #undef ZG_SSM
             ZG_SEQ_CHECK();
             return true;

@@ -1516,7 +1516,7 @@ static uint32_t attention_splits(const ZgSeqOp& s) {
     return S < 2 ? 1 : (S > 16 ? 16 : S);
 }
 size_t zg_seq_op_scratch_elems(const ZgOp& op, float* const* bufs) {
-    if (op.tag >= ZG_OP_SSM_SCAN) return 0;
+    if (op.tag >= ZG_OP_SSM_SCAN) return zg_rec_op_scratch_elems(op);
     if (op.tag >= ZG_OP_TOKEN_SHIFT) return zg_mix_op_scratch_elems(op);
     if (op.tag == ZG_OP_WINDOW_ATTENTION) {
         const uint32_t S = attention_splits(op.u.seq);
@@ -1731,6 +1731,6 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             return true;
         }
         default:
-            return op.tag >= ZG_OP_SSM_SCAN ? zg_launch_rec_op(op, bufs, st) : zg_launch_mix_op(op, bufs, scratch, st);
+            return op.tag >= ZG_OP_SSM_SCAN ? zg_launch_rec_op(op, bufs, scratch, st) : zg_launch_mix_op(op, bufs, scratch, st);
     }
 }

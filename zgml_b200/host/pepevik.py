@@ -206,7 +206,8 @@ class PepevikModel:
             self.buffers[i] = A.upload(be)
         A = WeightArena(self.wdt)
         emb, pos, head = tensors("embed"), tensors("pos"), tensors("head")
-        assert emb.shape == (cfg.vocab, D) and head.shape == (cfg.vocab, D) and pos.shape == (cfg.max_positions, D), f"pos: shape {pos.shape}"
+        assert emb.shape == (cfg.vocab, D) and head.shape == (cfg.vocab, D) and pos.ndim == 2 and pos.shape[1] == D and pos.shape[0] >= 1, f"pos: shape {pos.shape}"
+        self.positions = min(cfg.max_positions, pos.shape[0])      # a sequence can go as far as both the configuration and the table allow
         A.add("embed", emb)
         A.add("pos", pos)
         dyt(A, "final.norm", "final.norm")
@@ -229,7 +230,7 @@ class PepevikModel:
     # ── state ──
     def capacity(self, max_chunk: int, max_context: Optional[int]) -> int:
         """Positions a sequence of the session may reach: what the caller asks for, never more than the position table holds."""
-        return min(max(int(max_context) if max_context else DEFAULT_CONTEXT, max_chunk), self.cfg.max_positions)
+        return min(max(int(max_context) if max_context else DEFAULT_CONTEXT, max_chunk), self.positions)
 
     def _ssm_state_elems(self, m: dict) -> int:
         probe = DeviceOp.ssm_scan(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, m["heads"], m["groups"], m["state"], m["vdim"], 1, 1, self.wdt)
