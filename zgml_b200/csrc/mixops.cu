@@ -894,7 +894,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             return true;
         }
         case ZG_OP_CACHE_APPEND:
-            ZG_SEQ_WDT(s.n[5] ? s.n[7] : ZG_W_F32, launch_pdl(k_cache_append<WT>, dim3(s.n[0]), dim3(128), 0, st, bufs[s.buf[0]] + s.off[1], bufs[s.buf[1]] + s.off[0], bufs[s.buf[2]],
+            ZG_SEQ_WDT(s.n[5] ? s.n[7] : ZG_W_F32, launch_pdl(k_cache_append<WT>, dim3(s.n[0]), dim3(s.off[5] ? 256 : 128), 0, st, bufs[s.buf[0]] + s.off[1], bufs[s.buf[1]] + s.off[0], bufs[s.buf[2]],
                                                              s.n[5] ? wptr<WT>(bufs, s.buf[3], s.off[2]) : nullptr, s.n[1], s.n[2], s.n[3], s.n[4], s.n[5], s.n[6], s.n[8], s.f[0], s.f[1], s.n[9],
                                                              s.off[5] ? bufs[s.buf[1]] + s.off[3] : nullptr, s.off[5] ? wptr<WT>(bufs, s.buf[3], s.off[4]) : nullptr, s.off[5], s.off[6], s.f[2]));
             ZG_SEQ_CHECK();
