@@ -79,13 +79,14 @@ typedef enum ZgOpTag {
     ZG_OP_POLY_NORM = 30,
     /* Recurrent mixers with an elementwise or scalar decay, and what surrounds them (csrc/recops.cu): the state-space scan
      * of Mamba-2, the minimal gated recurrent unit, a gated group norm, a per-head RMS norm with a position-dependent
-     * query temperature, and stand-alone activations. */
+     * query temperature, stand-alone activations, and the real-gated linear recurrent unit. */
     ZG_OP_SSM_SCAN = 31,
     ZG_OP_MIN_GRU = 32,
     ZG_OP_GATED_NORM = 33,
     ZG_OP_HEAD_NORM = 34,
     ZG_OP_ACTIVATION = 35,
-    ZG_OP_END = 36
+    ZG_OP_RG_LRU = 36,
+    ZG_OP_END = 37
 } ZgOpTag;
 
 /* Parameter pack of the sequence-model ops.  buf[] are program buffer indices (ZG_NO_BUF: absent), off[] element offsets,
@@ -100,8 +101,10 @@ typedef enum ZgOpTag {
  * EMBED             dst[t, :] = table[ids[t], :] * f0; with n3 = 1 a learned position row joins it, unscaled: + positions[p(t), :]
  *                   (a second table at off 1 of the same arena, p(t) = the token's position in its sequence)
  *                   buf 0 dst 1 ctl 2 table | off 0 table 1 positions | n 0 T 1 D 2 wdt 3 positions | f 0 scale
- * LINEAR            dst[m, n] = act(sum_k src[m, k] W[n, k] (+ bias[n])); act (n6): 0 none, 1 + the ACTIVATION kind otherwise
+ * LINEAR            dst[m, n] = act(sum_k src[m, k] W[n, k] (+ bias[n])); act (n6): 0 none, 1 + the ACTIVATION kind otherwise (f0: its
+ *                   parameter, where the kind has one)
  *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt 6 act
+ *                   f 0 activation parameter
  * NORM              dst = (res +) norm(src) * w ; kind bit 0 clear: (x - mean) / sqrt(var + eps), set: x / sqrt(mean(x^2) + eps);
  *                   kind bit 1: the weight is stored around zero and applied as (1 + w); kind bit 2: the result is also
  *                   multiplied by the gain f1 (a scale of the following product folded into its input);
@@ -144,7 +147,14 @@ typedef enum ZgOpTag {
  *                   off 0 q 1 k 2 v (columns of a qkv row) 3 beta (column of its row) 4 A_log 5 dt_bias 6 norm_w (weights)
  *                   7 gate (column of its row)
  *                   n 0 T 1 H 2 G 3 dim 4 vdim 5 qkv row stride 6 beta row stride 7 a row stride 8 gate row stride 9 wdt
- *                   f 0 output-norm eps 1 unit-vector eps 2 q scale
+ *                   10 form 11 dst row stride (0: H * vdim) 12 dst column
+ *                   f 0 output-norm eps 1 unit-vector eps 2 q scale 3 decay temperature 4 output scale (0: 1)
+ *                   Form bits (n10), all clear for the rule above.  Bit 0, plain accumulation (gated linear attention): no
+ *                   unit vectors (q is only scaled by f2) and no correction by what the state already holds, u = v:
+ *                   S <- g * S + k v^T, o = S^T q; buf 2 is not read.  Bit 1: the decay is g = sigmoid(a + dt_bias)^(1 / f3),
+ *                   evaluated as exp(-softplus(-(a + dt_bias)) / f3); A_log is not read.  Bit 2: the output gate is
+ *                   silu(gate) instead of sigmoid(gate).  The result is multiplied by f4 and may land in columns of a wider
+ *                   row (n11, n12), beside another mixer's heads.
  * ROUTE             mode 0: s = softmax(logits) over all NE outputs; the `top` largest of s + correction are chosen (ties:
  *                   lowest index); dst[t, c] = {index as int32 bits, s[index]} (weights not renormalised)
  *                   mode 1: z = logits + correction (a bias); the `top` largest z are chosen (ties: lowest index) and weighted
@@ -167,9 +177,10 @@ typedef enum ZgOpTag {
  *                   buf 0 dst 1 hist 2 coeff | off 0 coeff | n 0 elements 1 terms 2 stride 3 wdt
  * ROTARY            rotary positions on `heads` vectors per row, in place or (buf 2) read from another buffer: layout 0 pairs
  *                   (2i, 2i + 1), layout 1 pairs (i, i + dims / 2); pair i of the token at position p turns by
- *                   p * base^(-2i / dims).  Angles in f32.
- *                   buf 0 x 1 ctl 2 src | off 0 column of the first vector 1 its column in src | n 0 T 1 heads 2 head stride
- *                   3 row stride 4 dims 5 layout 6 src head stride 7 src row stride | f 0 base
+ *                   p * base^(-2i / dims), or, with buf 3, by p * table[i]: dims / 2 frequencies in f32 (any schedule: scaled,
+ *                   blended, interpolated), in a buffer of the model at element off 2.  Angles in f32.
+ *                   buf 0 x 1 ctl 2 src 3 frequency table | off 0 column of the first vector 1 its column in src 2 table offset
+ *                   n 0 T 1 heads 2 head stride 3 row stride 4 dims 5 layout 6 src head stride 7 src row stride | f 0 base
  * CACHE_APPEND      the step's rows join a per-sequence cache (external [slots, R, width]; position p lives in row p mod R).
  *                   Of the appended columns the first `normed` are RMS-normed with a plain weight (a latent), the next `rot`
  *                   get the token's rotary position (a key part shared by all heads), the rest is copied.  With n9 > 0 the
@@ -189,8 +200,16 @@ typedef enum ZgOpTag {
  *                   (any distance bias; a constant per head folds into it).  Weights (off 5): 0 softmax over the visible keys,
  *                   1 sigmoid(score) of every visible key, not normalised over the keys.
  *                   buf 0 dst [T, H * maps, dv] 1 q 2 key cache 3 value cache 4 ctl 5 score table
+ *                   With f1 > 0 the scaled score is capped smoothly first: f1 * tanh(s / f1).  With buf 6 a learned SINK per
+ *                   (head, map) joins the softmax: exp(sink) is added to the denominator alone; it has no key and no value, is
+ *                   neither scaled nor capped, and counts once (a weight operand: element off 7 of buf 6, type n12).  The
+ *                   result is multiplied by f2 (0: 1) and may land in columns of a wider row (n10 row stride, 0: H * maps * dv;
+ *                   n11 first column), beside another mixer's heads.
+ *                   buf 0 dst [T, H * maps, dv] 1 q 2 key cache 3 value cache 4 ctl 5 score table 6 sinks
  *                   off 0 q column 1 key column 2 value column (inside a cache row) 3 mask kind 4 mask size 5 weights 6 table row length
- *                   n 0 T 1 H 2 G 3 maps 4 dk 5 dv 6 q row stride 7 key row width 8 value row width 9 R | f 0 score scale
+ *                   7 sinks
+ *                   n 0 T 1 H 2 G 3 maps 4 dk 5 dv 6 q row stride 7 key row width 8 value row width 9 R 10 dst row stride
+ *                   11 dst column 12 wdt of the sinks | f 0 score scale 1 score cap 2 output scale
  * MAP_COMBINE       differential attention's combination of two maps: o = a[.., 0, :] - f0 * a[.., 1, :], then
  *                   o / sqrt(mean(o^2) + f1) * f2 per (token, head)
  *                   buf 0 dst [rows, dv] 1 src [rows, 2, dv] | n 0 rows 1 dv | f 0 lambda 1 eps 2 output scale
@@ -223,8 +242,18 @@ typedef enum ZgOpTag {
  *                   grows with the position p of the token: 1 + f1 * ln(floor((p + 1) / n5) + 1) (n5 = 0: none)
  *                   buf 0 x 1 w 2 ctl | off 0 column of the first head 1 w | n 0 T 1 heads 2 dim 3 row stride 4 wdt 5 period
  *                   f 0 eps 1 temperature coefficient
- * ACTIVATION        dst = act(src) element by element, may run in place; kinds: 0 relu(z)^2, 1 silu, 2 gelu (tanh form), 3 relu
- *                   buf 0 dst 1 src | n 0 elements 1 kind */
+ * ACTIVATION        dst = act(src) element by element, may run in place; kinds: 0 relu(z)^2, 1 silu, 2 gelu (tanh form), 3 relu,
+ *                   4 smooth cap f0 * tanh(z / f0)
+ *                   buf 0 dst 1 src | n 0 elements 1 kind | f 0 parameter of the kind
+ * RG_LRU            real-gated linear recurrent unit, element by element over W channels: r = sigmoid(rl + r_bias),
+ *                   i = sigmoid(il + i_bias), log a = -f0 * r * softplus(lam), S <- a S + sqrt(1 - a^2) (i u) (external
+ *                   [slots, W], zeros for a fresh slot; the first token is no special case), dst = S * act(y) (n9: 0 the
+ *                   column itself, 1 + the ACTIVATION kind otherwise).  The gate logits rl | il come from a block-diagonal
+ *                   product: channel c lies at column (c / n4) * n5 + c % n4 of its row, from off 1 (rl) and off 2 (il).
+ *                   buf 0 dst 1 u 2 gate logits 3 y 4 weights 5 state 6 ctl
+ *                   off 0 u column 1 rl column 2 il column 3 y column 4 r_bias 5 i_bias 6 lam (weights)
+ *                   n 0 T 1 W 2 u row stride 3 gate row stride 4 gate block width 5 gate block stride 6 y row stride
+ *                   7 dst row stride 8 wdt 9 act of y | f 0 the constant in log a */
 #define ZG_NO_BUF 0xFFFFFFFFu
 #define ZG_W_F32 0
 #define ZG_W_BF16 1
@@ -234,8 +263,8 @@ typedef enum ZgOpTag {
 typedef struct ZgSeqOp {
     uint32_t buf[8];
     uint32_t off[8];
-    uint32_t n[10];
-    float f[4];
+    uint32_t n[16];
+    float f[8];
 } ZgSeqOp;
 
 /* MatMulGeometry — reference src/backend.zig:146-158 (all usize). */

@@ -22,13 +22,14 @@ OP_ALLREDUCE, OP_ALLGATHER = 12, 13   # multi-GPU extensions (need comm_init)
 (OP_EMBED, OP_LINEAR, OP_NORM, OP_WINDOW_ATTENTION, OP_CAUSAL_CONV, OP_DELTA_RULE, OP_ROUTE, OP_MOE_FFN) = range(14, 22)
 (OP_TOKEN_SHIFT, OP_DEPTH_MIX, OP_ROTARY, OP_CACHE_APPEND, OP_CACHED_ATTENTION, OP_MAP_COMBINE, OP_GATE, OP_HEAD_LINEAR,
  OP_POLY_NORM) = range(22, 31)
-(OP_SSM_SCAN, OP_MIN_GRU, OP_GATED_NORM, OP_HEAD_NORM, OP_ACTIVATION) = range(31, 36)
-OP_END = 36
+(OP_SSM_SCAN, OP_MIN_GRU, OP_GATED_NORM, OP_HEAD_NORM, OP_ACTIVATION, OP_RG_LRU) = range(31, 37)
+OP_END = 37
 MASK_CAUSAL, MASK_WINDOW, MASK_BLOCK = 0, 1, 2
 NORM_LAYER, NORM_RMS, NORM_UNIT_OFFSET, NORM_GAIN = 0, 1, 2, 4
 NORM_DYNAMIC_TANH, NORM_NONE = 8, 16       # tanh(alpha x) w + b (bias and alpha follow w); the row itself: no statistics either way
+DELTA_PLAIN, DELTA_SIGMOID_DECAY, DELTA_SILU_GATE = 1, 2, 4     # forms of DELTA_RULE (n10)
 WEIGHTS_SOFTMAX, WEIGHTS_SIGMOID = 0, 1    # CACHED_ATTENTION: normalised over the visible keys, or sigmoid(score) of each
-ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "relu": 3}
+ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "relu": 3, "softcap": 4}     # "softcap": p * tanh(z / p), p the op's activation parameter
 NO_BUF = 0xFFFFFFFF
 W_F32, W_BF16 = 0, 1
 CTL_POS, CTL_SLOT, CTL_IDS = 0, 1, 8
@@ -115,7 +116,7 @@ class _AllGather(C.Structure):
 
 
 class ZgSeqOp(C.Structure):
-    _fields_ = [("buf", u32 * 8), ("off", u32 * 8), ("n", u32 * 10), ("f", f32 * 4)]
+    _fields_ = [("buf", u32 * 8), ("off", u32 * 8), ("n", u32 * 16), ("f", f32 * 8)]
 class _OpUnion(C.Union):
     _fields_ = [("elementwise", _Elementwise), ("matmul", _MatMul), ("qmatmul", _QMatMul),
                 ("softmax", _Softmax), ("layernorm", _Norm), ("rmsnorm", _Norm), ("reduce", _Reduce),

@@ -212,10 +212,10 @@ class DeviceOp:
         return DeviceOp._seq(abi.OP_EMBED, [dst, ctl, table], [table_off, positions_off or 0], [T, D, wdt, int(positions_off is not None)], [scale])
 
     @staticmethod
-    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0, act=None):
-        """`act`: an activation of abi.ACTIVATIONS applied in the epilogue, after the bias."""
+    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0, act=None, act_param=0.0):
+        """`act`: an activation of abi.ACTIVATIONS applied in the epilogue, after the bias (`act_param`: its parameter, where it has one)."""
         return DeviceOp._seq(abi.OP_LINEAR, [dst, src, w, bias], [w_off, bias_off, src_off, dst_off],
-                             [M, N, K, src_rs or K, dst_rs or N, wdt, 0 if act is None else abi.ACTIVATIONS[act] + 1])
+                             [M, N, K, src_rs or K, dst_rs or N, wdt, 0 if act is None else abi.ACTIVATIONS[act] + 1], [act_param])
 
     @staticmethod
     def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer",
@@ -266,10 +266,16 @@ class DeviceOp:
 
     @staticmethod
     def delta_rule(dst, qkv, beta, a, gate, w, state, ctl, q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off,
-                   T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, norm_eps, unit_eps, q_scale, gate_off=0):
+                   T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, norm_eps, unit_eps, q_scale, gate_off=0, plain=False, decay_tau=None,
+                   silu_gate=False, out_scale=0.0, dst_rs=0, dst_col=0):
+        """`plain`: no unit vectors and no correction by the state (S <- g S + k v^T: gated linear attention; `beta` may be None).
+        `decay_tau`: the decay is sigmoid(a + dt_bias)^(1 / tau) instead of exp(-exp(A_log) softplus(a + dt_bias)).  `silu_gate`: the
+        output gate is silu instead of sigmoid.  `out_scale` multiplies the result, which may land at column `dst_col` of rows
+        `dst_rs` wide."""
+        form = (abi.DELTA_PLAIN if plain else 0) | (abi.DELTA_SIGMOID_DECAY if decay_tau is not None else 0) | (abi.DELTA_SILU_GATE if silu_gate else 0)
         return DeviceOp._seq(abi.OP_DELTA_RULE, [dst, qkv, beta, a, gate, w, state, ctl],
                              [q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off, gate_off],
-                             [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt], [norm_eps, unit_eps, q_scale])
+                             [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, form, dst_rs, dst_col], [norm_eps, unit_eps, q_scale, decay_tau or 0.0, out_scale])
 
     @staticmethod
     def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0, mode="corrected_softmax", groups=0, groups_kept=0):
@@ -295,8 +301,9 @@ class DeviceOp:
         return DeviceOp._seq(abi.OP_DEPTH_MIX, [dst, hist, w], [coeff_off], [n, terms, stride, wdt])
 
     @staticmethod
-    def rotary(x, ctl, col, T, heads, head_stride, row_stride, dims, base, layout="pairs", src=None, src_col=0, src_hs=0, src_rs=0):
-        return DeviceOp._seq(abi.OP_ROTARY, [x, ctl, src], [col, src_col],
+    def rotary(x, ctl, col, T, heads, head_stride, row_stride, dims, base, layout="pairs", src=None, src_col=0, src_hs=0, src_rs=0, freqs=None, freqs_off=0):
+        """`freqs`: an f32 buffer with dims / 2 frequencies at element `freqs_off`, used instead of base^(-2i / dims)."""
+        return DeviceOp._seq(abi.OP_ROTARY, [x, ctl, src, freqs], [col, src_col, freqs_off],
                              [T, heads, head_stride, row_stride, dims, {"pairs": 0, "halves": 1}[layout], src_hs, src_rs], [base])
 
     @staticmethod
@@ -310,13 +317,16 @@ class DeviceOp:
 
     @staticmethod
     def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,
-                         mask="causal", mask_size=0, weights="softmax", score_table=None, table_len=0):
+                         mask="causal", mask_size=0, weights="softmax", score_table=None, table_len=0, softcap=0.0, sink=None, sink_off=0, sink_wdt=0,
+                         out_scale=0.0, dst_rs=0, dst_col=0):
         """`score_table`: an f32 buffer [H * maps, table_len] added to the scaled scores by distance; `weights` "sigmoid": every
-        visible key weighs sigmoid(score), not normalised over the keys."""
+        visible key weighs sigmoid(score), not normalised over the keys.  `softcap` > 0: the scaled score passes cap * tanh(s / cap).
+        `sink`: a weight buffer with one learned score per (head, map) at `sink_off` whose exponential joins the softmax's denominator.
+        `out_scale` multiplies the result, which may land at column `dst_col` of rows `dst_rs` wide."""
         kinds = {"causal": abi.MASK_CAUSAL, "window": abi.MASK_WINDOW, "block": abi.MASK_BLOCK}
-        return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl, score_table],
-                             [q_col, k_col, v_col, kinds[mask], mask_size, {"softmax": abi.WEIGHTS_SOFTMAX, "sigmoid": abi.WEIGHTS_SIGMOID}[weights], table_len],
-                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows], [scale])
+        return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl, score_table, sink],
+                             [q_col, k_col, v_col, kinds[mask], mask_size, {"softmax": abi.WEIGHTS_SOFTMAX, "sigmoid": abi.WEIGHTS_SIGMOID}[weights], table_len, sink_off],
+                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, dst_rs, dst_col, sink_wdt], [scale, softcap, out_scale])
 
     @staticmethod
     def map_combine(dst, src, rows, dv, lam, eps, out_scale):
@@ -354,8 +364,16 @@ class DeviceOp:
         return DeviceOp._seq(abi.OP_HEAD_NORM, [x, w, ctl], [col, w_off], [T, heads, dim, row_stride, wdt, temp_every], [eps, temp_coef])
 
     @staticmethod
-    def activation(dst, src, n, kind):
-        return DeviceOp._seq(abi.OP_ACTIVATION, [dst, src], [], [n, abi.ACTIVATIONS[kind]])
+    def activation(dst, src, n, kind, param=0.0):
+        return DeviceOp._seq(abi.OP_ACTIVATION, [dst, src], [], [n, abi.ACTIVATIONS[kind]], [param])
+
+    @staticmethod
+    def rg_lru(dst, u, gates, y, w, state, ctl, u_col, r_col, i_col, y_col, r_bias_off, i_bias_off, lam_off, T, W, u_rs, gate_rs, gate_bw, gate_bs, y_rs, wdt,
+               rate=8.0, y_act=None, dst_rs=0):
+        """Real-gated linear recurrent unit over W channels.  The gate logits of channel c lie at column (c // gate_bw) * gate_bs +
+        c % gate_bw of a `gates` row, from r_col and i_col; biases and `lam` are weights; `y_act` is applied to y on its way out."""
+        return DeviceOp._seq(abi.OP_RG_LRU, [dst, u, gates, y, w, state, ctl], [u_col, r_col, i_col, y_col, r_bias_off, i_bias_off, lam_off],
+                             [T, W, u_rs, gate_rs, gate_bw, gate_bs, y_rs, dst_rs or W, wdt, 0 if y_act is None else abi.ACTIVATIONS[y_act] + 1], [rate])
 
 
 @dataclass

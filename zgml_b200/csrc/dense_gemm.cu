@@ -84,8 +84,9 @@ __global__ void k_to_bf16(const float* __restrict__ x, uint32_t x_rs, uint32_t* 
 }
 
 // the epilogue's activation (the kinds of the ACTIVATION op, shifted by one: 0 is none)
-__device__ __forceinline__ float gemm_act(float z, uint32_t act) {
+__device__ __forceinline__ float gemm_act(float z, uint32_t act, float p) {
     switch (act) {
+        case 5: return p * tanhf(z / p);
         case 0: return z;
         case 1: { const float r = fmaxf(z, 0.0f); return r * r; }
         case 2: return z / (1.0f + expf(-z));
@@ -97,7 +98,8 @@ struct GemmParams {
     float* out;
     const __nv_bfloat16* bias;
     uint32_t M, N, K, out_rs, out_vec4;
-    uint32_t act;            // applied after the bias: 0 none, 1 relu^2, 2 silu, 3 gelu (tanh form), 4 relu
+    uint32_t act;            // applied after the bias: 0 none, 1 relu^2, 2 silu, 3 gelu (tanh form), 4 relu, 5 smooth cap act_p * tanh(z / act_p)
+    float act_p;
     const int* tile_group;   // GROUPED: weight matrix (third TMA coordinate) of every 128-row tile, -1: tile unused
 };
 
@@ -203,15 +205,15 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     for (int it = 0; it < 8; it++) {
                         const uint32_t rr = it * 4 + (lane >> 3), mm = m_base + rr;
                         const uint4 o = tb[rr * 9 + (lane & 7)];
-                        const float4 f = make_float4((ACT ? gemm_act(__uint_as_float(o.x) + b[0], p.act) : __uint_as_float(o.x) + b[0]), (ACT ? gemm_act(__uint_as_float(o.y) + b[1], p.act) : __uint_as_float(o.y) + b[1]), (ACT ? gemm_act(__uint_as_float(o.z) + b[2], p.act) : __uint_as_float(o.z) + b[2]),
-                                                     (ACT ? gemm_act(__uint_as_float(o.w) + b[3], p.act) : __uint_as_float(o.w) + b[3]));
+                        const float4 f = make_float4((ACT ? gemm_act(__uint_as_float(o.x) + b[0], p.act, p.act_p) : __uint_as_float(o.x) + b[0]), (ACT ? gemm_act(__uint_as_float(o.y) + b[1], p.act, p.act_p) : __uint_as_float(o.y) + b[1]), (ACT ? gemm_act(__uint_as_float(o.z) + b[2], p.act, p.act_p) : __uint_as_float(o.z) + b[2]),
+                                                     (ACT ? gemm_act(__uint_as_float(o.w) + b[3], p.act, p.act_p) : __uint_as_float(o.w) + b[3]));
                         if (mm < p.M) *reinterpret_cast<float4*>(p.out + (size_t)mm * p.out_rs + nn) = f;
                     }
                 } else if (n0 + lane < p.N) {
                     const uint32_t* tw = reinterpret_cast<const uint32_t*>(tb);
                     const float b = p.bias ? __bfloat162float(p.bias[n0 + lane]) : 0.0f;
                     for (int rr = 0; rr < 32; rr++)
-                        if (m_base + rr < p.M) p.out[(size_t)(m_base + rr) * p.out_rs + n0 + lane] = (ACT ? gemm_act(__uint_as_float(tw[rr * 36 + lane]) + b, p.act) : __uint_as_float(tw[rr * 36 + lane]) + b);
+                        if (m_base + rr < p.M) p.out[(size_t)(m_base + rr) * p.out_rs + n0 + lane] = (ACT ? gemm_act(__uint_as_float(tw[rr * 36 + lane]) + b, p.act, p.act_p) : __uint_as_float(tw[rr * 36 + lane]) + b);
                 }
             }
             __syncwarp();
@@ -265,7 +267,7 @@ unsigned int zg_dense_gemm_timeouts() {
 }
 
 bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float* src, float* dst, uint32_t M, uint32_t N, uint32_t K,
-                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act) {
+                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act, float act_p) {
     if (!prepare()) return false;
     const uint32_t Kp = (K + BK - 1) / BK * BK, Mp = (M + BM - 1) / BM * BM;
     uint32_t* xb = reinterpret_cast<uint32_t*>(scratch);
@@ -290,7 +292,7 @@ bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float
         if (r != CUDA_SUCCESS) { zg_set_error("cuTensorMapEncodeTiled(weights) failed (%d)", (int)r); return false; }
     }
     GemmParams p;
-    p.out = dst; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_bf16); p.M = M; p.N = N; p.K = K; p.out_rs = dst_rs; p.act = act;
+    p.out = dst; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_bf16); p.M = M; p.N = N; p.K = K; p.out_rs = dst_rs; p.act = act; p.act_p = act_p;
     p.out_vec4 = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && (dst_rs & 3) == 0) ? 1u : 0u;
     p.tile_group = nullptr;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
@@ -325,7 +327,7 @@ bool zg_dense_gemm_grouped_launch(const void* w_bf16, uint32_t groups, const voi
         if (r != CUDA_SUCCESS) { zg_set_error("cuTensorMapEncodeTiled(stacked weights) failed (%d)", (int)r); return false; }
     }
     GemmParams p;
-    p.out = dst; p.bias = nullptr; p.M = rows; p.N = N; p.K = K; p.out_rs = dst_rs; p.act = 0;
+    p.out = dst; p.bias = nullptr; p.M = rows; p.N = N; p.K = K; p.out_rs = dst_rs; p.act = 0; p.act_p = 0.0f;
     p.out_vec4 = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0 && (dst_rs & 3) == 0) ? 1u : 0u;
     p.tile_group = d_tile_group;
     dim3 grid((N + BN - 1) / BN, rows / BM);

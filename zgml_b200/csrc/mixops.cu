@@ -44,15 +44,17 @@ __device__ __forceinline__ void rotary_angle(uint32_t pos, uint32_t i, uint32_t 
     const float freq = (float)pow((double)base, -2.0 * (double)i / (double)dims);
     sincosf((float)pos * freq, &sn, &cs);
 }
+// With `freqs` (dims / 2 values) the pair's frequency comes from that table: a schedule the caller evaluated.
 __global__ void k_rotary(float* x, const float* src, const float* __restrict__ ctl, uint32_t T, uint32_t heads, uint32_t head_stride,
-                         uint32_t row_stride, uint32_t dims, uint32_t layout, uint32_t src_hs, uint32_t src_rs, float base) {
+                         uint32_t row_stride, uint32_t dims, uint32_t layout, uint32_t src_hs, uint32_t src_rs, float base, const float* __restrict__ freqs) {
     pdl_enter();
     const uint32_t half = dims / 2;
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= (size_t)T * heads * half) return;
     const uint32_t i = (uint32_t)(e % half), hd = (uint32_t)((e / half) % heads), t = (uint32_t)(e / ((size_t)half * heads));
     float sn, cs;
-    rotary_angle((uint32_t)ctl_word(ctl, ZG_CTL_POS) + t, i, dims, base, sn, cs);
+    if (freqs) sincosf((float)((uint32_t)ctl_word(ctl, ZG_CTL_POS) + t) * freqs[i], &sn, &cs);
+    else rotary_angle((uint32_t)ctl_word(ctl, ZG_CTL_POS) + t, i, dims, base, sn, cs);
     float* v = x + (size_t)t * row_stride + (size_t)hd * head_stride;
     const float* sv = src + (size_t)t * src_rs + (size_t)hd * src_hs;
     const uint32_t a = layout == 0 ? 2 * i : i, b = layout == 0 ? 2 * i + 1 : i + half;
@@ -125,7 +127,24 @@ struct CaArgs {
     float scale;
     const float* tab;      // score table [H * maps, tab_rs] by distance, or null
     uint32_t tab_rs, wkind;   // weights: 0 softmax over the visible keys, 1 sigmoid of every visible key (not normalised)
+    float cap;             // > 0: the scaled score passes cap * tanh(s / cap)
+    const void* sink;      // a learned score per (head, map) that joins the softmax's denominator only, or null
+    uint32_t sink_bf16;    // its weight type
+    float out_scale;       // the result is multiplied by it
+    uint32_t dst_rs;       // row stride of dst (its first column is folded into the pointer)
 };
+__device__ __forceinline__ float ca_score(const CaArgs& a, float dot) {
+    const float s = dot * a.scale;
+    return a.cap > 0.0f ? a.cap * tanhf(s / a.cap) : s;
+}
+__device__ __forceinline__ float ca_sink(const CaArgs& a, uint32_t hm) {
+    return a.sink_bf16 ? __bfloat162float(reinterpret_cast<const bf16*>(a.sink)[hm]) : reinterpret_cast<const float*>(a.sink)[hm];
+}
+// 1 / (sum + exp(sink - max)): the sink's share of the denominator, in the frame of the running maximum
+__device__ __forceinline__ float ca_inv_sum(const CaArgs& a, uint32_t hm, float mx, float l) {
+    if (a.sink) l += expf(ca_sink(a, hm) - mx);
+    return 1.0f / l;
+}
 // weight of a visible key under the unnormalised kind
 __device__ __forceinline__ float ca_sigmoid(float s) { return __frcp_rn(1.0f + expf(-s)); }
 constexpr int kCaMaxDv = 1024;   // 32 channels per lane in the per-query kernel
@@ -157,7 +176,7 @@ __global__ void k_cached_attention(CaArgs a) {
             const float* k = kbase + (size_t)(j % a.R) * a.kw;
             float d = 0.0f;
             for (uint32_t c = 0; c < a.dk; c++) d = fmaf(q[c], k[c], d);
-            s = d * a.scale;
+            s = ca_score(a, d);
             if (a.tab) s += a.tab[(size_t)hm * a.tab_rs + (p - j)];
         }
         float corr = 1.0f, e;
@@ -182,8 +201,8 @@ __global__ void k_cached_attention(CaArgs a) {
             }
         }
     }
-    const float inv = a.wkind ? 1.0f : 1.0f / l;
-    float* out = a.dst + ((size_t)t * HM + hm) * a.dv;
+    const float inv = (a.wkind ? 1.0f : ca_inv_sum(a, hm, mx, l)) * a.out_scale;
+    float* out = a.dst + (size_t)t * a.dst_rs + (size_t)hm * a.dv;
 #pragma unroll
     for (int i = 0; i < kCaMaxDv / 32; i++) {
         const uint32_t c = lane + 32 * i;
@@ -332,7 +351,7 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
             for (int c = 0; c < 4; c++) {
                 const uint32_t j = s0 + tx + 16 * c;
                 const bool seen = ok_r[r] && j <= p_r[r] && j >= lo_r[r] && j < k_end;
-                float sv = seen ? sc[r][c] * a.scale : -INFINITY;
+                float sv = seen ? ca_score(a, sc[r][c]) : -INFINITY;
                 if (seen && tab_r[r]) sv += tab_r[r][p_r[r] - j];
                 sc[r][c] = sv;
                 rmax = fmaxf(rmax, sv);
@@ -380,8 +399,8 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
         if (!ok_r[r]) continue;
         const uint32_t hm = (g * rh + row % rh) * a.maps + m;
         if (splits == 1) {
-            const float inv = a.wkind ? 1.0f : 1.0f / l_run[r];         // every query sees itself
-            float* out = a.dst + ((size_t)(row / rh) * a.H * a.maps + hm) * a.dv + (size_t)vs * DV;
+            const float inv = (a.wkind ? 1.0f : ca_inv_sum(a, hm, m_run[r], l_run[r])) * a.out_scale;         // every query sees itself
+            float* out = a.dst + (size_t)(row / rh) * a.dst_rs + (size_t)hm * a.dv + (size_t)vs * DV;
 #pragma unroll
             for (int c = 0; c < OC; c++) if (tx + 16 * c < v_cols) out[tx + 16 * c] = o[r][c] * inv;
         } else {
@@ -394,19 +413,21 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
 }
 // merge of the key shares: CTA (x, y) = 128 value columns y of (token, head, map) x; a share that saw no key carries
 // max = -inf and weighs nothing (its output is zero)
-__global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restrict__ dst, const float* __restrict__ part, uint32_t dv, uint32_t splits,
+// (a: for the sink, the output scale and the row layout of dst; HM = H * maps)
+__global__ void __launch_bounds__(128) k_cached_attention_merge(CaArgs a, const float* __restrict__ part, uint32_t dv, uint32_t splits,
                                                                 uint32_t wkind) {
     pdl_enter();
     __shared__ float w[kCtMaxSplits];
     const float* P = part + (size_t)blockIdx.x * splits * (4 + dv);
+    const uint32_t HM = a.H * a.maps, hm = blockIdx.x % HM;
     if (wkind) {                                       // unnormalised weights: the shares just add up
-        if (threadIdx.x < splits) w[threadIdx.x] = 1.0f;
+        if (threadIdx.x < splits) w[threadIdx.x] = a.out_scale;
     } else if (threadIdx.x < 32) {                            // warp 0: the shares' weights exp(m_i - M) / L
         float m0 = threadIdx.x < splits ? P[threadIdx.x * (4 + dv)] : -INFINITY, m1 = threadIdx.x + 32 < splits ? P[(threadIdx.x + 32) * (4 + dv)] : -INFINITY;
         float l0 = threadIdx.x < splits ? P[threadIdx.x * (4 + dv) + 1] : 0.0f, l1 = threadIdx.x + 32 < splits ? P[(threadIdx.x + 32) * (4 + dv) + 1] : 0.0f;
         const float M = warp_max(fmaxf(m0, m1));
         const float e0 = m0 == -INFINITY ? 0.0f : expf(m0 - M), e1 = m1 == -INFINITY ? 0.0f : expf(m1 - M);
-        const float inv = 1.0f / warp_sum(l0 * e0 + l1 * e1);
+        const float inv = ca_inv_sum(a, hm, M, warp_sum(l0 * e0 + l1 * e1)) * a.out_scale;
         if (threadIdx.x < splits) w[threadIdx.x] = e0 * inv;
         if (threadIdx.x + 32 < splits) w[threadIdx.x + 32] = e1 * inv;
     }
@@ -416,7 +437,7 @@ __global__ void __launch_bounds__(128) k_cached_attention_merge(float* __restric
     float acc = 0.0f;
 #pragma unroll 4
     for (uint32_t i = 0; i < splits; i++) acc = fmaf(P[i * (4 + dv) + 4 + c], w[i], acc);
-    dst[(size_t)blockIdx.x * dv + c] = acc;
+    a.dst[(size_t)(blockIdx.x / HM) * a.dst_rs + (size_t)hm * dv + c] = acc;
 }
 
 // Few query rows (decoding: tokens x heads of a key group <= 16): what bounds the step is the latency of pulling the cache,
@@ -513,7 +534,7 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
 #pragma unroll
             for (int w = 0; w < kCfParts; w++) d += Sp[(w * kCfRows + row) * kCfKeys + kk];
             const bool seen = ok && kk < nk && j <= p_r && j >= lo_r;
-            sv[u] = seen ? d * a.scale : -INFINITY;
+            sv[u] = seen ? ca_score(a, d) : -INFINITY;
             if (seen && tab_r) sv[u] += tab_r[p_r - j];
         }
         float rmax = fmaxf(sv[0], sv[1]);
@@ -556,7 +577,7 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
         }
     }
     __syncthreads();
-    if (kq == 0) Al[row] = a.wkind ? 1.0f : (l_run > 0.0f ? 1.0f / l_run : 0.0f);
+    if (kq == 0) Al[row] = (a.wkind ? 1.0f : (l_run > 0.0f ? ca_inv_sum(a, (g * rh + (ok ? row % rh : 0)) * a.maps + m, m_run, l_run) : 0.0f)) * a.out_scale;
     if (splits > 1 && kq == 0 && ok) {
         float* mine = part + (((size_t)(row / rh) * a.H * a.maps + (g * rh + row % rh) * a.maps + m) * splits + blockIdx.y) * (4 + a.dv);
         mine[0] = m_run; mine[1] = l_run;
@@ -565,12 +586,13 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
 #pragma unroll
     for (int r = 0; r < kCfRows; r++) {
         if ((uint32_t)r >= total) break;
-        const size_t item = (size_t)((uint32_t)r / rh) * a.H * a.maps + (g * rh + (uint32_t)r % rh) * a.maps + m;
+        const uint32_t hm_r = (g * rh + (uint32_t)r % rh) * a.maps + m;
+        const size_t item = (size_t)((uint32_t)r / rh) * a.H * a.maps + hm_r;
 #pragma unroll
         for (int i = 0; i < CI; i++) {
             const uint32_t c = tid + kCfThreads * i;
             if (c >= a.dv) continue;
-            if (splits == 1) a.dst[item * a.dv + c] = acc[r][i] * Al[r];
+            if (splits == 1) a.dst[(size_t)((uint32_t)r / rh) * a.dst_rs + (size_t)hm_r * a.dv + c] = acc[r][i] * Al[r];
             else part[(item * splits + blockIdx.y) * (4 + a.dv) + 4 + c] = acc[r][i];
         }
     }
@@ -781,7 +803,8 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         }
         case ZG_OP_ROTARY: {
             const size_t T = s.n[0], heads = s.n[1], hs = s.n[2], rs = s.n[3], dims = s.n[4];
-            if (!T || !heads || !dims || dims % 2 || hs < dims || s.n[5] > 1 || !(s.f[0] > 0.0f)) return fail("rotary: shape");
+            if (!T || !heads || !dims || dims % 2 || hs < dims || s.n[5] > 1 || (s.buf[3] == ZG_NO_BUF && !(s.f[0] > 0.0f))) return fail("rotary: shape");
+            if (s.buf[3] != ZG_NO_BUF && !fits(3, s.off[2], dims / 2)) return fail("rotary: frequency table");
             if (s.off[0] + (heads - 1) * hs + dims > rs) return fail("rotary: columns");
             if (!fits(0, 0, (T - 1) * rs + s.off[0] + (heads - 1) * hs + dims) || !fits(1, 0, ZG_CTL_IDS)) return fail("rotary: extent");
             if (s.buf[2] != ZG_NO_BUF) {
@@ -812,7 +835,10 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!T || !H || !G || H % G || !maps || !dk || !dv || dv > kCaMaxDv || kind > 2 || (kind && !size)) return fail("cached_attention: shape");
             if (R < T) return fail("cached_attention: cache rows");   // the caller sizes R for what the mask reaches and bounds the positions
             if (s.off[0] + H * maps * dk > qrs || s.off[1] + G * maps * dk > kw || s.off[2] + G * dv > vw) return fail("cached_attention: columns");
-            if (!fits(0, 0, T * H * maps * dv) || !fits(1, 0, (T - 1) * qrs + s.off[0] + H * maps * dk) || !have(2) || elems[s.buf[2]] < R * kw || !have(3) ||
+            const size_t drs = s.n[10] ? s.n[10] : H * maps * dv;
+            if (s.n[11] + H * maps * dv > drs || s.f[1] < 0.0f) return fail("cached_attention: destination columns or cap");
+            if (s.buf[6] != ZG_NO_BUF && (s.off[5] || !wfits(6, s.n[12], s.off[7], H * maps))) return fail("cached_attention: sinks");
+            if (!fits(0, 0, (T - 1) * drs + s.n[11] + H * maps * dv) || !fits(1, 0, (T - 1) * qrs + s.off[0] + H * maps * dk) || !have(2) || elems[s.buf[2]] < R * kw || !have(3) ||
                 elems[s.buf[3]] < R * vw || !fits(4, 0, ZG_CTL_IDS))
                 return fail("cached_attention: extent");
             if (s.buf[0] == s.buf[1]) return fail("cached_attention: in place");
@@ -889,7 +915,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             float* x = bufs[s.buf[0]] + s.off[0];
             const bool sep = s.buf[2] != ZG_NO_BUF;
             launch_pdl(k_rotary, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, x, sep ? bufs[s.buf[2]] + s.off[1] : x, bufs[s.buf[1]], s.n[0], s.n[1], s.n[2], s.n[3], s.n[4], s.n[5],
-                       sep ? s.n[6] : s.n[2], sep ? s.n[7] : s.n[3], s.f[0]);
+                       sep ? s.n[6] : s.n[2], sep ? s.n[7] : s.n[3], s.f[0], s.buf[3] != ZG_NO_BUF ? (const float*)(bufs[s.buf[3]] + s.off[2]) : (const float*)nullptr);
             ZG_SEQ_CHECK();
             return true;
         }
@@ -905,6 +931,9 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.maps = s.n[3]; a.dk = s.n[4]; a.dv = s.n[5]; a.q_rs = s.n[6]; a.q_off = s.off[0];
             a.kw = s.n[7]; a.k_off = s.off[1]; a.vw = s.n[8]; a.v_off = s.off[2]; a.R = s.n[9]; a.kind = s.off[3]; a.size = s.off[4]; a.scale = s.f[0];
             a.tab = s.buf[5] != ZG_NO_BUF ? bufs[s.buf[5]] : nullptr; a.tab_rs = s.off[6]; a.wkind = s.off[5];
+            a.cap = s.f[1]; a.out_scale = s.f[2] != 0.0f ? s.f[2] : 1.0f; a.dst_rs = s.n[10] ? s.n[10] : a.H * a.maps * a.dv; a.dst += s.n[11];
+            a.sink = nullptr; a.sink_bf16 = s.n[12] == ZG_W_BF16;
+            if (s.buf[6] != ZG_NO_BUF) a.sink = a.sink_bf16 ? (const void*)wptr<bf16>(bufs, s.buf[6], s.off[7]) : (const void*)wptr<float>(bufs, s.buf[6], s.off[7]);
             const bool aligned = ca_aligned(s) && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
             if (aligned && ca_few(s)) {
                 const uint32_t S = scratch ? ca_splits(s) : 1, alias = cf_alias(s) ? 1u : 0u;
@@ -921,7 +950,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
 #undef ZG_CF
                 if (S > 1) {
                     ZG_SEQ_CHECK();
-                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S, a.wkind);
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a, (const float*)part, a.dv, S, a.wkind);
                 }
             } else if (aligned) {
                 const uint32_t S = scratch ? ca_splits(s) : 1;
@@ -942,7 +971,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
                 }
                 if (S > 1) {
                     ZG_SEQ_CHECK();
-                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a.dst, (const float*)part, a.dv, S, a.wkind);
+                    launch_pdl(k_cached_attention_merge, dim3(a.T * a.H * a.maps, (a.dv + 127) / 128), dim3(128), 0, st, a, (const float*)part, a.dv, S, a.wkind);
                 }
             } else {
                 const uint32_t warps = 4, items = a.T * a.H * a.maps;

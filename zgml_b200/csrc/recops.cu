@@ -1,4 +1,4 @@
-// Sequence-model DeviceOps ZG_OP_SSM_SCAN .. ZG_OP_ACTIVATION (parameter packs in include/zgml_cuda.h): recurrent mixers
+// Sequence-model DeviceOps ZG_OP_SSM_SCAN .. ZG_OP_RG_LRU (parameter packs in include/zgml_cuda.h): recurrent mixers
 // whose decay is a scalar per head (the state-space scan of Mamba-2) or a gate per element (the minimal gated recurrent
 // unit), the gated group norm that closes the former, a per-head RMS norm with a position-dependent temperature, and
 // stand-alone activations.  Everything here is f32: step sizes, softplus and exponentials, decays, gates, the states and
@@ -245,43 +245,81 @@ static uint32_t ssm_segments(uint32_t T, uint32_t H, uint32_t N, uint32_t P, uin
     return (T + len - 1) / len;
 }
 
-// ── MIN_GRU ──────────────────────────────────────────────────────────────────────────────────────────────────────
-// S_t = (1 - z_t) S_{t-1} + z_t c_t is a linear recurrence per channel whose coefficients do not depend on the state, so the
-// step's tokens are cut into up to 64 segments that are walked side by side: thread (channel, segment) first walks its segment
-// from an empty state, keeping the product of the (1 - z) and the value reached; the segments' (product, value) pairs are then
+// ── MIN_GRU, RG_LRU: gated recurrences per channel ───────────────────────────────────────────────────────────────
+// S_t = a_t S_{t-1} + b_t is a linear recurrence per channel whose coefficients do not depend on the state, so the step's
+// tokens are cut into up to 64 segments that are walked side by side: thread (channel, segment) first walks its segment
+// from an empty state, keeping the product of the a_t and the value reached; the segments' (product, value) pairs are then
 // folded in order, which gives every segment the state it starts from; the second walk writes the outputs.  A single-token
-// step is one segment of one token.
+// step is one segment of one token.  A CELL names the recurrence: what it reads per (token, channel), what it keeps per
+// channel, how a token advances (product, state), and what leaves the unit.
 constexpr int kGruChannels = 16, kGruMaxSegments = 64;
-__global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_min_gru(float* __restrict__ dst, const float* __restrict__ proj, float* __restrict__ state,
-                                                                            const float* __restrict__ ctl, uint32_t T, uint32_t W, uint32_t rs, uint32_t drs,
-                                                                            uint32_t z_off, uint32_t u_off, uint32_t g_off, uint32_t seg_len) {
+// minimal gated recurrent unit: z = sigmoid(zl), candidate u + 1/2 (u >= 0) or sigmoid(u), S <- (1 - z) S + z c, out = S silu(g)
+struct MinGruCell {
+    const float* proj; uint32_t rs, z_off, u_off, g_off;
+    struct Chan {};
+    struct Raw { float zl, u, gl; };
+    __device__ __forceinline__ Chan channel(uint32_t) const { return Chan(); }
+    __device__ __forceinline__ Raw load(uint32_t t, uint32_t c, bool out) const {
+        const float* row = proj + (size_t)t * rs;
+        Raw r; r.zl = row[z_off + c]; r.u = row[u_off + c]; r.gl = out ? row[g_off + c] : 0.0f;
+        return r;
+    }
+    __device__ __forceinline__ void step(const Chan&, const Raw& r, float& A, float& S) const {
+        const float z = sigmoidf_(r.zl), cand = r.u >= 0.0f ? r.u + 0.5f : sigmoidf_(r.u);
+        A *= 1.0f - z;
+        S = fmaf(z, cand, (1.0f - z) * S);
+    }
+    __device__ __forceinline__ float out(const Raw& r, float S) const { return S * (r.gl * sigmoidf_(r.gl)); }
+};
+// real-gated linear recurrent unit: r = sigmoid(rl + br), i = sigmoid(il + bi), log a = -c r softplus(lam),
+// S <- a S + sqrt(1 - a^2) (i u), out = S act(y).  1 - a^2 = -expm1(2 log a) keeps its digits where a is close to 1.
+template <typename WT>
+struct RgLruCell {
+    const float* u; const float* gates; const float* y; const WT* wts;
+    uint32_t u_rs, u_off, g_rs, r_off, i_off, g_bw, g_bs, y_rs, y_off, rb_off, ib_off, lam_off, act;
+    float c;
+    struct Chan { float br, bi, rate; uint32_t gcol; };
+    struct Raw { float rl, il, u, y; };
+    __device__ __forceinline__ Chan channel(uint32_t ch) const {
+        Chan k; k.br = wld(wts, (size_t)rb_off + ch); k.bi = wld(wts, (size_t)ib_off + ch); k.rate = c * softplusf_(wld(wts, (size_t)lam_off + ch));
+        k.gcol = (ch / g_bw) * g_bs + ch % g_bw;
+        return k;
+    }
+    __device__ __forceinline__ Raw load(uint32_t t, uint32_t ch, bool out) const {
+        const uint32_t gcol = (ch / g_bw) * g_bs + ch % g_bw;
+        const float* g = gates + (size_t)t * g_rs + gcol;
+        Raw r; r.rl = g[r_off]; r.il = g[i_off]; r.u = u[(size_t)t * u_rs + u_off + ch]; r.y = out ? y[(size_t)t * y_rs + y_off + ch] : 0.0f;
+        return r;
+    }
+    __device__ __forceinline__ void step(const Chan& k, const Raw& r, float& A, float& S) const {
+        const float la = -k.rate * sigmoidf_(r.rl + k.br), a = expf(la);
+        A *= a;
+        S = fmaf(a, S, sqrtf(-expm1f(2.0f * la)) * (sigmoidf_(r.il + k.bi) * r.u));
+    }
+    __device__ __forceinline__ float out(const Raw& r, float S) const { return S * seq_epilogue(r.y, act); }
+};
+template <typename Cell>
+__global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_channel_scan(Cell cell, float* __restrict__ dst, float* __restrict__ state,
+                                                                                 const float* __restrict__ ctl, uint32_t T, uint32_t W, uint32_t drs, uint32_t seg_len) {
     pdl_enter();
     __shared__ float segA[kGruMaxSegments][kGruChannels], segB[kGruMaxSegments][kGruChannels];
     const uint32_t c = blockIdx.x * kGruChannels + threadIdx.x, seg = threadIdx.y, n_seg = blockDim.y;
     const bool on = c < W;
     const uint32_t t_begin = min(T, seg * seg_len), t_end = min(T, t_begin + seg_len);
     float* st = state + (size_t)ctl_word(ctl, ZG_CTL_SLOT) * W;
+    const typename Cell::Chan chan = cell.channel(on ? c : 0);
     float S = 0.0f;
     constexpr int U = 8;                                   // tokens whose loads are in flight together
     if (n_seg > 1) {
         float A = 1.0f;
         if (on)
             for (uint32_t t = t_begin; t < t_end; t += U) {
-                float zl[U], u[U];
+                typename Cell::Raw raw[U];
 #pragma unroll
-                for (int i = 0; i < U; i++) {
-                    const float* row = proj + (size_t)min(t + i, t_end - 1) * rs;
-                    zl[i] = row[z_off + c];
-                    u[i] = row[u_off + c];
-                }
+                for (int i = 0; i < U; i++) raw[i] = cell.load(min(t + i, t_end - 1), c, false);
 #pragma unroll
-                for (int i = 0; i < U; i++) {
-                    if (t + i < t_end) {
-                        const float z = sigmoidf_(zl[i]), cand = u[i] >= 0.0f ? u[i] + 0.5f : sigmoidf_(u[i]);
-                        A *= 1.0f - z;
-                        S = fmaf(z, cand, (1.0f - z) * S);
-                    }
-                }
+                for (int i = 0; i < U; i++)
+                    if (t + i < t_end) cell.step(chan, raw[i], A, S);
             }
         segA[seg][threadIdx.x] = A;
         segB[seg][threadIdx.x] = S;
@@ -291,24 +329,26 @@ __global__ void __launch_bounds__(kGruChannels * kGruMaxSegments) k_min_gru(floa
     S = st[c];
     for (uint32_t j = 0; j < seg; j++) S = fmaf(segA[j][threadIdx.x], S, segB[j][threadIdx.x]);
     for (uint32_t t = t_begin; t < t_end; t += U) {
-        float zl[U], u[U], gl[U];
+        typename Cell::Raw raw[U];
 #pragma unroll
-        for (int i = 0; i < U; i++) {
-            const float* row = proj + (size_t)min(t + i, t_end - 1) * rs;
-            zl[i] = row[z_off + c];
-            u[i] = row[u_off + c];
-            gl[i] = row[g_off + c];
-        }
+        for (int i = 0; i < U; i++) raw[i] = cell.load(min(t + i, t_end - 1), c, true);
 #pragma unroll
         for (int i = 0; i < U; i++) {
             if (t + i < t_end) {
-                const float z = sigmoidf_(zl[i]), cand = u[i] >= 0.0f ? u[i] + 0.5f : sigmoidf_(u[i]);
-                S = fmaf(z, cand, (1.0f - z) * S);
-                dst[(size_t)(t + i) * drs + c] = S * (gl[i] * sigmoidf_(gl[i]));
+                float A = 1.0f;
+                cell.step(chan, raw[i], A, S);
+                dst[(size_t)(t + i) * drs + c] = cell.out(raw[i], S);
             }
         }
     }
     if (seg == n_seg - 1) st[c] = S;
+}
+// segments of a step of T tokens: four tokens or more each, no empty one at the end (the last leaves the state behind)
+static uint32_t scan_segments(uint32_t T, uint32_t* seg_len) {
+    uint32_t n_seg = (T + 3) / 4;
+    if (n_seg > (uint32_t)kGruMaxSegments) n_seg = kGruMaxSegments;
+    *seg_len = (T + n_seg - 1) / n_seg;
+    return (T + *seg_len - 1) / *seg_len;
 }
 
 // ── GATED_NORM: one CTA per (token, group) ───────────────────────────────────────────────────────────────────────
@@ -376,17 +416,17 @@ __global__ void k_head_norm(float* x, const WT* __restrict__ w, const float* __r
 // ── ACTIVATION ───────────────────────────────────────────────────────────────────────────────────────────────────
 // four elements per thread (n a multiple of 4, both buffers on 16-byte boundaries) or one
 template <bool VEC>
-__global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t kind) {
+__global__ void k_activation(float* dst, const float* src, uint32_t n, uint32_t kind, float p) {
     pdl_enter();
     const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
         if (4 * e >= n) return;
         float4 v = reinterpret_cast<const float4*>(src)[e];
-        v.x = seq_activation(v.x, kind); v.y = seq_activation(v.y, kind); v.z = seq_activation(v.z, kind); v.w = seq_activation(v.w, kind);
+        v.x = seq_activation(v.x, kind, p); v.y = seq_activation(v.y, kind, p); v.z = seq_activation(v.z, kind, p); v.w = seq_activation(v.w, kind, p);
         reinterpret_cast<float4*>(dst)[e] = v;
     } else {
         if (e >= n) return;
-        dst[e] = seq_activation(src[e], kind);
+        dst[e] = seq_activation(src[e], kind, p);
     }
 }
 
@@ -447,8 +487,20 @@ bool zg_rec_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!fits(0, 0, (T - 1) * rs + s.off[0] + heads * dim) || !wfits(1, s.n[4], s.off[1], dim) || !fits(2, 0, ZG_CTL_IDS)) return fail("head_norm: extent");
             return true;
         }
+        case ZG_OP_RG_LRU: {
+            const size_t T = s.n[0], W = s.n[1], urs = s.n[2], grs = s.n[3], bw = s.n[4], bs = s.n[5], yrs = s.n[6], drs = s.n[7];
+            if (!T || !W || !bw || W % bw || bs < bw || drs < W || s.n[9] > 5 || !(s.f[0] > 0.0f)) return fail("rg_lru: shape");
+            const size_t gspan = (W / bw - 1) * bs + bw;
+            if (s.off[0] + W > urs || s.off[1] + gspan > grs || s.off[2] + gspan > grs || s.off[3] + W > yrs) return fail("rg_lru: columns");
+            if (!fits(0, 0, (T - 1) * drs + W) || !fits(1, 0, (T - 1) * urs + s.off[0] + W) || !fits(2, 0, (T - 1) * grs + (s.off[1] > s.off[2] ? s.off[1] : s.off[2]) + gspan) ||
+                !fits(3, 0, (T - 1) * yrs + s.off[3] + W) || !wfits(4, s.n[8], s.off[4], W) || !wfits(4, s.n[8], s.off[5], W) || !wfits(4, s.n[8], s.off[6], W) || !have(5) ||
+                elems[s.buf[5]] < W || !fits(6, 0, ZG_CTL_IDS))
+                return fail("rg_lru: extent");
+            if (s.buf[0] == s.buf[1] || s.buf[0] == s.buf[2] || s.buf[0] == s.buf[3]) return fail("rg_lru: in place");
+            return true;
+        }
         case ZG_OP_ACTIVATION: {
-            if (!s.n[0] || s.n[1] > 3) return fail("activation: shape");
+            if (!s.n[0] || s.n[1] > 4 || (s.n[1] == 4 && !(s.f[0] > 0.0f))) return fail("activation: shape");
             if (!fits(0, 0, s.n[0]) || !fits(1, 0, s.n[0])) return fail("activation: extent");
             return true;
         }
@@ -460,6 +512,7 @@ uint32_t zg_rec_op_writes(uint32_t tag) {
     switch (tag) {
         case ZG_OP_SSM_SCAN: return 1u | (1u << 4);
         case ZG_OP_MIN_GRU: return 1u | (1u << 2);
+        case ZG_OP_RG_LRU: return 1u | (1u << 5);
         default: return 1u;
     }
 }
@@ -521,12 +574,27 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
         }
         case ZG_OP_MIN_GRU: {
             const uint32_t T = s.n[0];
-            uint32_t n_seg = (T + 3) / 4;
-            if (n_seg > (uint32_t)kGruMaxSegments) n_seg = kGruMaxSegments;
-            const uint32_t seg_len = (T + n_seg - 1) / n_seg;
-            n_seg = (T + seg_len - 1) / seg_len;            // no empty segment at the end: the last one leaves the state behind
-            launch_pdl_if(T < (uint32_t)kLongWalk, k_min_gru, dim3((s.n[1] + kGruChannels - 1) / kGruChannels), dim3(kGruChannels, n_seg), 0, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]],
-                       T, s.n[1], s.n[2], s.n[3], s.off[0], s.off[1], s.off[2], seg_len);
+            uint32_t seg_len;
+            const uint32_t n_seg = scan_segments(T, &seg_len);
+            MinGruCell cell;
+            cell.proj = bufs[s.buf[1]]; cell.rs = s.n[2]; cell.z_off = s.off[0]; cell.u_off = s.off[1]; cell.g_off = s.off[2];
+            launch_pdl_if(T < (uint32_t)kLongWalk, k_channel_scan<MinGruCell>, dim3((s.n[1] + kGruChannels - 1) / kGruChannels), dim3(kGruChannels, n_seg), 0, st, cell, bufs[s.buf[0]], bufs[s.buf[2]],
+                          (const float*)bufs[s.buf[3]], T, s.n[1], s.n[3], seg_len);
+            ZG_SEQ_CHECK();
+            return true;
+        }
+        case ZG_OP_RG_LRU: {
+            const uint32_t T = s.n[0];
+            uint32_t seg_len;
+            const uint32_t n_seg = scan_segments(T, &seg_len);
+            ZG_SEQ_WDT(s.n[8], {
+                RgLruCell<WT> cell;
+                cell.u = bufs[s.buf[1]]; cell.gates = bufs[s.buf[2]]; cell.y = bufs[s.buf[3]]; cell.wts = wptr<WT>(bufs, s.buf[4], 0);
+                cell.u_rs = s.n[2]; cell.u_off = s.off[0]; cell.g_rs = s.n[3]; cell.r_off = s.off[1]; cell.i_off = s.off[2]; cell.g_bw = s.n[4]; cell.g_bs = s.n[5];
+                cell.y_rs = s.n[6]; cell.y_off = s.off[3]; cell.rb_off = s.off[4]; cell.ib_off = s.off[5]; cell.lam_off = s.off[6]; cell.act = s.n[9]; cell.c = s.f[0];
+                launch_pdl_if(T < (uint32_t)kLongWalk, k_channel_scan<RgLruCell<WT>>, dim3((s.n[1] + kGruChannels - 1) / kGruChannels), dim3(kGruChannels, n_seg), 0, st, cell, bufs[s.buf[0]],
+                              bufs[s.buf[5]], (const float*)bufs[s.buf[6]], T, s.n[1], s.n[7], seg_len);
+            });
             ZG_SEQ_CHECK();
             return true;
         }
@@ -547,9 +615,9 @@ bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
         }
         case ZG_OP_ACTIVATION:
             if (s.n[0] % 4 == 0 && ((reinterpret_cast<uintptr_t>(bufs[s.buf[0]]) | reinterpret_cast<uintptr_t>(bufs[s.buf[1]])) & 15) == 0)
-                launch_pdl(k_activation<true>, dim3((s.n[0] / 4 + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], (const float*)bufs[s.buf[1]], s.n[0], s.n[1]);
+                launch_pdl(k_activation<true>, dim3((s.n[0] / 4 + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], (const float*)bufs[s.buf[1]], s.n[0], s.n[1], s.f[0]);
             else
-                launch_pdl(k_activation<false>, dim3((s.n[0] + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], (const float*)bufs[s.buf[1]], s.n[0], s.n[1]);
+                launch_pdl(k_activation<false>, dim3((s.n[0] + 255) / 256), dim3(256), 0, st, bufs[s.buf[0]], (const float*)bufs[s.buf[1]], s.n[0], s.n[1], s.f[0]);
             ZG_SEQ_CHECK();
             return true;
         default:

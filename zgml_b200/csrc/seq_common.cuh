@@ -60,17 +60,19 @@ inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ int ctl_word(const float* ctl, int i) { return reinterpret_cast<const int*>(ctl)[i]; }
-// the activations of ACTIVATION and of LINEAR's epilogue: 0 relu(z)^2, 1 silu, 2 gelu (tanh form), 3 relu
-__device__ __forceinline__ float seq_activation(float z, uint32_t kind) {
+// the activations of ACTIVATION and of LINEAR's epilogue: 0 relu(z)^2, 1 silu, 2 gelu (tanh form), 3 relu, 4 smooth cap
+// p * tanh(z / p) (p: the op's activation parameter)
+__device__ __forceinline__ float seq_activation(float z, uint32_t kind, float p = 0.0f) {
     switch (kind) {
         case 0: { const float r = fmaxf(z, 0.0f); return r * r; }
         case 1: return z * sigmoidf_(z);
         case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+        case 4: return p * tanhf(z / p);
         default: return fmaxf(z, 0.0f);
     }
 }
 // epilogue form: act = 0 none, kind + 1 otherwise
-__device__ __forceinline__ float seq_epilogue(float z, uint32_t act) { return act ? seq_activation(z, act - 1) : z; }
+__device__ __forceinline__ float seq_epilogue(float z, uint32_t act, float p = 0.0f) { return act ? seq_activation(z, act - 1, p) : z; }
 
 // 16-byte weight loads (8 bf16 / 4 f32 per lane and trip) when the row start and K allow it
 template <typename WT> struct WVec;

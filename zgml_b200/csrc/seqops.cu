@@ -32,7 +32,7 @@ __global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, 
 constexpr int kGemvRows = 8;
 template <typename WT>
 __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
-                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
+                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act, float act_p) {
     pdl_enter();
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (n >= N) return;
@@ -51,7 +51,7 @@ __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__
     for (int m = 0; m < kGemvRows; m++) {
         if (m < (int)M) {
             const float s = warp_sum(acc[m]);
-            if (lane == 0) dst[(size_t)m * dst_rs + n] = seq_epilogue(s + b, act);
+            if (lane == 0) dst[(size_t)m * dst_rs + n] = seq_epilogue(s + b, act, act_p);
         }
     }
 }
@@ -59,7 +59,7 @@ __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__
 // vectors per lane are in flight per trip.
 template <typename WT, int MR>
 __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
-                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act) {
+                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act, float act_p) {
     // Weights are constants of the model, so this warp's weight row is pulled toward L2 BEFORE the wait on the predecessor:
     // in a replayed graph the HBM stream of a matvec starts under the tail of the kernel that produces its input.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -124,7 +124,7 @@ __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restri
     for (int m = 0; m < MR; m++) {
         if (m < (int)M) {
             const float s = warp_sum(acc[m]);
-            if (lane == 0) dst[(size_t)m * dst_rs + n] = seq_epilogue(s + b, act);
+            if (lane == 0) dst[(size_t)m * dst_rs + n] = seq_epilogue(s + b, act, act_p);
         }
     }
 }
@@ -134,7 +134,7 @@ constexpr int kTM = 64, kTN = 64, kTK = 16;
 template <typename WT>
 __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W,
                                                      const WT* __restrict__ bias, uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs,
-                                                     uint32_t dst_rs, uint32_t act) {
+                                                     uint32_t dst_rs, uint32_t act, float act_p) {
     __shared__ float As[kTK][kTM + 4];
     __shared__ float Ws[kTK][kTN + 4];
     const uint32_t m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, co
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint32_t n = n0 + tx * 4 + j;
-            if (n < N) dst[(size_t)m * dst_rs + n] = seq_epilogue(acc[i][j] + (bias ? wld(bias, n) : 0.0f), act);
+            if (n < N) dst[(size_t)m * dst_rs + n] = seq_epilogue(acc[i][j] + (bias ? wld(bias, n) : 0.0f), act, act_p);
         }
     }
 }
@@ -844,14 +844,23 @@ __global__ void k_conv_advance(float* __restrict__ state, const float* __restric
 // adjacent lanes and meet by shuffles.  The per-token vectors (unit k, scaled unit q, decay) of kDeltaTile tokens are
 // prepared by the whole CTA at once, then the tokens are walked without further barriers.
 constexpr int kDeltaRows = 16, kDeltaTile = 16, kDeltaThreads = 128;
+// forms of the rule (op parameter n10): plain accumulation without unit vectors and correction (gated linear attention), the
+// decay as a tempered sigmoid, a SiLU output gate
+constexpr uint32_t kDeltaPlain = 1, kDeltaSigmoidDecay = 2, kDeltaSiluGate = 4;
+// decay of one key channel from its logit z (the bias is already added): exp(-exp(A) softplus(z)), or sigmoid(z)^(1 / tau) =
+// exp(-softplus(-z) / tau)
+__device__ __forceinline__ float delta_decay(float z, float Ah, uint32_t form, float inv_tau) {
+    return (form & kDeltaSigmoidDecay) ? expf(-softplusf_(-z) * inv_tau) : expf(-Ah * softplusf_(z));
+}
 template <typename WT>
 __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
     float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ betab, const float* __restrict__ ab, const WT* __restrict__ wts,
     float* __restrict__ state, const float* __restrict__ ctl, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t vdim, uint32_t RS,
     uint32_t q_off, uint32_t k_off, uint32_t v_off, uint32_t beta_off, uint32_t A_off, uint32_t dt_off, uint32_t qkv_rs, uint32_t beta_rs,
-    uint32_t a_rs, float unit_eps, float q_scale) {
+    uint32_t a_rs, float unit_eps, float q_scale, uint32_t form, float inv_tau, uint32_t dst_rs) {
     pdl_enter();
     extern __shared__ float sm[];
+    const bool plain = form & kDeltaPlain;             // no unit vectors, no correction: S <- g S + k v^T
     const uint32_t dpad = RS * kDeltaRows;             // rows incl. padding (k = q = 0, decay = 1 there)
     float* sk = sm;                                    // [tile][dpad]
     float* sq = sk + kDeltaTile * dpad;
@@ -869,7 +878,7 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
         const uint32_t row = r * kDeltaRows + i;
         S[i] = (live && row < dim) ? S_g[(size_t)row * vdim + col] : 0.0f;
     }
-    const float Ah = expf(wld(wts, (size_t)A_off + h));
+    const float Ah = (form & kDeltaSigmoidDecay) ? 0.0f : expf(wld(wts, (size_t)A_off + h));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (uint32_t t0 = 0; t0 < T; t0 += kDeltaTile) {
         const uint32_t nt = min((uint32_t)kDeltaTile, T - t0);
@@ -880,16 +889,19 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
             const float* qr = qkv + (size_t)t * qkv_rs + q_off + (size_t)kv * dim;
             const float* kr = qkv + (size_t)t * qkv_rs + k_off + (size_t)kv * dim;
             const float* ar = ab + (size_t)t * a_rs + (size_t)h * dim;
-            float qq = 0.0f, kk = 0.0f;
-            for (uint32_t c = lane; c < dim; c += 32) { qq = fmaf(qr[c], qr[c], qq); kk = fmaf(kr[c], kr[c], kk); }
-            const float qn = q_scale / sqrtf(warp_sum(qq) + unit_eps), kn = 1.0f / sqrtf(warp_sum(kk) + unit_eps);
+            float qn = q_scale, kn = 1.0f;
+            if (!plain) {
+                float qq = 0.0f, kk = 0.0f;
+                for (uint32_t c = lane; c < dim; c += 32) { qq = fmaf(qr[c], qr[c], qq); kk = fmaf(kr[c], kr[c], kk); }
+                qn = q_scale / sqrtf(warp_sum(qq) + unit_eps); kn = 1.0f / sqrtf(warp_sum(kk) + unit_eps);
+            }
             for (uint32_t c = lane; c < dpad; c += 32) {
                 const bool in = c < dim;
                 sk[tt * dpad + c] = in ? kr[c] * kn : 0.0f;
                 sq[tt * dpad + c] = in ? qr[c] * qn : 0.0f;
-                sg[tt * dpad + c] = in ? expf(-Ah * softplusf_(ar[c] + wld(wts, (size_t)dt_off + (size_t)h * dim + c))) : 1.0f;
+                sg[tt * dpad + c] = in ? delta_decay(ar[c] + wld(wts, (size_t)dt_off + (size_t)h * dim + c), Ah, form, inv_tau) : 1.0f;
             }
-            if (lane == 0) sbeta[tt] = sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h]);
+            if (lane == 0) sbeta[tt] = plain ? 1.0f : sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h]);
         }
         float vt[kDeltaTile];                              // the tile's values of this column: independent loads, issued together
 #pragma unroll
@@ -908,13 +920,13 @@ __global__ void __launch_bounds__(kDeltaThreads) k_delta_rule(
             float ks = 0.0f;
 #pragma unroll
             for (int i = 0; i < kDeltaRows; i++) { S[i] *= g[i]; ks = fmaf(S[i], k[i], ks); }
-            for (uint32_t o = 1; o < RS; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
-            const float u = sbeta[tt] * (v - ks);
+            if (!plain) for (uint32_t o = 1; o < RS; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
+            const float u = plain ? v : sbeta[tt] * (v - ks);
             float os = 0.0f;
 #pragma unroll
             for (int i = 0; i < kDeltaRows; i++) { S[i] = fmaf(k[i], u, S[i]); os = fmaf(S[i], q[i], os); }
             for (uint32_t o = 1; o < RS; o <<= 1) os += __shfl_xor_sync(0xffffffffu, os, o);
-            if (live && r == 0) dst[((size_t)t * H + h) * vdim + col] = os;
+            if (live && r == 0) dst[(size_t)t * dst_rs + (size_t)h * vdim + col] = os;
         }
     }
 #pragma unroll
@@ -947,8 +959,9 @@ template <typename WT>
 __global__ void k_delta_prepare(float* __restrict__ prep, const float* __restrict__ qkv, const float* __restrict__ betab, const float* __restrict__ ab,
                                 const WT* __restrict__ wts, uint32_t T, uint32_t H, uint32_t G, uint32_t dim, uint32_t dpad, uint32_t q_off,
                                 uint32_t k_off, uint32_t beta_off, uint32_t A_off, uint32_t dt_off, uint32_t qkv_rs, uint32_t beta_rs, uint32_t a_rs,
-                                float unit_eps, float q_scale) {
+                                float unit_eps, float q_scale, uint32_t form, float inv_tau) {
     pdl_enter();
+    const bool plain = form & kDeltaPlain;
     const uint32_t w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= T * H) return;
     const uint32_t t = w / H, h = w % H, kv = h / (H / G);
@@ -957,25 +970,26 @@ __global__ void k_delta_prepare(float* __restrict__ prep, const float* __restric
     const float* ar = ab + (size_t)t * a_rs + (size_t)h * dim;
     float qq = 0.0f, kk = 0.0f, qk = 0.0f;
     for (uint32_t c = lane; c < dim; c += 32) { const float a = qr[c], b = kr[c]; qq = fmaf(a, a, qq); kk = fmaf(b, b, kk); qk = fmaf(a, b, qk); }
-    const float qn = q_scale / sqrtf(warp_sum(qq) + unit_eps), kn = 1.0f / sqrtf(warp_sum(kk) + unit_eps);
+    const float qn = plain ? q_scale : q_scale / sqrtf(warp_sum(qq) + unit_eps), kn = plain ? 1.0f : 1.0f / sqrtf(warp_sum(kk) + unit_eps);
     qk = warp_sum(qk) * qn * kn;
-    const float Ah = expf(wld(wts, (size_t)A_off + h));
+    const float Ah = (form & kDeltaSigmoidDecay) ? 0.0f : expf(wld(wts, (size_t)A_off + h));
     float* row = prep + ((size_t)h * T + t) * (3 * dpad + 4);
     for (uint32_t c = lane; c < dpad; c += 32) {
         const bool in = c < dim;
         row[c] = in ? kr[c] * kn : 0.0f;
         row[dpad + c] = in ? qr[c] * qn : 0.0f;
-        row[2 * dpad + c] = in ? expf(-Ah * softplusf_(ar[c] + wld(wts, (size_t)dt_off + (size_t)h * dim + c))) : 1.0f;
+        row[2 * dpad + c] = in ? delta_decay(ar[c] + wld(wts, (size_t)dt_off + (size_t)h * dim + c), Ah, form, inv_tau) : 1.0f;
     }
-    if (lane < 4) row[3 * dpad + lane] = lane == 0 ? sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h]) : (lane == 1 ? qk : 0.0f);
+    if (lane < 4) row[3 * dpad + lane] = lane == 0 ? (plain ? 1.0f : sigmoidf_(betab[(size_t)t * beta_rs + beta_off + h])) : (lane == 1 ? qk : 0.0f);
 }
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
 }
-template <uint32_t RS>                                 // row slices of a column: compile-time, so the shuffle steps unroll
+// PLAIN: the accumulation without correction (u = v), which needs no product with k and only one reduction per token
+template <uint32_t RS, bool PLAIN>                     // row slices of a column: compile-time, so the shuffle steps unroll
 __global__ void __launch_bounds__(kWalkThreads) k_delta_walk(float* __restrict__ dst, const float* __restrict__ qkv, const float* __restrict__ prep,
                                                                float* __restrict__ state, const float* __restrict__ ctl, uint32_t T, uint32_t H,
-                                                               uint32_t dim, uint32_t vdim, uint32_t v_off, uint32_t qkv_rs) {
+                                                               uint32_t dim, uint32_t vdim, uint32_t v_off, uint32_t qkv_rs, uint32_t dst_rs) {
     pdl_enter();
     extern __shared__ __align__(16) float sm[];
     const uint32_t dpad = RS * kWalkRows, stride = 3 * dpad + 4, tile_elems = kDeltaTile * stride;
@@ -1027,21 +1041,23 @@ __global__ void __launch_bounds__(kWalkThreads) k_delta_walk(float* __restrict__
                 const float4 q4 = *reinterpret_cast<const float4*>(row + dpad + at);
                 g4[c] = *reinterpret_cast<const float4*>(row + 2 * dpad + at);
                 S[4 * c + 0] *= g4[c].x; S[4 * c + 1] *= g4[c].y; S[4 * c + 2] *= g4[c].z; S[4 * c + 3] *= g4[c].w;
-                ks0 = fmaf(S[4 * c + 0], k4[c].x, ks0); ks1 = fmaf(S[4 * c + 1], k4[c].y, ks1);
-                ks0 = fmaf(S[4 * c + 2], k4[c].z, ks0); ks1 = fmaf(S[4 * c + 3], k4[c].w, ks1);
+                if (!PLAIN) {
+                    ks0 = fmaf(S[4 * c + 0], k4[c].x, ks0); ks1 = fmaf(S[4 * c + 1], k4[c].y, ks1);
+                    ks0 = fmaf(S[4 * c + 2], k4[c].z, ks0); ks1 = fmaf(S[4 * c + 3], k4[c].w, ks1);
+                }
                 qs0 = fmaf(S[4 * c + 0], q4.x, qs0); qs1 = fmaf(S[4 * c + 1], q4.y, qs1);
                 qs0 = fmaf(S[4 * c + 2], q4.z, qs0); qs1 = fmaf(S[4 * c + 3], q4.w, qs1);
             }
             float ks = ks0 + ks1, qs = qs0 + qs1;
 #pragma unroll
-            for (uint32_t o = 1; o < RS; o <<= 1) { ks += __shfl_xor_sync(0xffffffffu, ks, o); qs += __shfl_xor_sync(0xffffffffu, qs, o); }
-            const float u = beta * (v - ks);
+            for (uint32_t o = 1; o < RS; o <<= 1) { if (!PLAIN) ks += __shfl_xor_sync(0xffffffffu, ks, o); qs += __shfl_xor_sync(0xffffffffu, qs, o); }
+            const float u = PLAIN ? v : beta * (v - ks);
 #pragma unroll
             for (int c = 0; c < kWalkRows / 4; c++) {
                 S[4 * c + 0] = fmaf(k4[c].x, u, S[4 * c + 0]); S[4 * c + 1] = fmaf(k4[c].y, u, S[4 * c + 1]);
                 S[4 * c + 2] = fmaf(k4[c].z, u, S[4 * c + 2]); S[4 * c + 3] = fmaf(k4[c].w, u, S[4 * c + 3]);
             }
-            if (live && r == 0) dst[((size_t)(t0 + tti) * H + h) * vdim + col] = fmaf(u, kq, qs);
+            if (live && r == 0) dst[(size_t)(t0 + tti) * dst_rs + (size_t)h * vdim + col] = fmaf(u, kq, qs);
         };
         if (nt == (uint32_t)kDeltaTile) {                  // a full tile: straight-line code, nothing between the tokens
 #pragma unroll
@@ -1063,20 +1079,20 @@ __global__ void __launch_bounds__(kWalkThreads) k_delta_walk(float* __restrict__
         if (live && row < dim) S_g[(size_t)row * vdim + col] = S[i];
     }
 }
-// o / rms(o) * norm_w * sigmoid(gate), one warp per (token, head), in place
+// o / rms(o) * norm_w * sigmoid(gate) (or silu(gate)) * out_scale, one warp per (token, head), in place
 template <typename WT>
 __global__ void k_delta_out(float* __restrict__ dst, const float* __restrict__ gate, const WT* __restrict__ wts, uint32_t TH, uint32_t H,
-                            uint32_t vdim, uint32_t gate_rs, uint32_t nw_off, float eps) {
+                            uint32_t vdim, uint32_t gate_rs, uint32_t nw_off, float eps, uint32_t dst_rs, uint32_t silu_gate, float out_scale) {
     pdl_enter();
     const uint32_t item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= TH) return;
     const uint32_t t = item / H, h = item % H;
-    float* o = dst + (size_t)item * vdim;
+    float* o = dst + (size_t)t * dst_rs + (size_t)h * vdim;
     const float* g = gate + (size_t)t * gate_rs + (size_t)h * vdim;
     float q = 0.0f;
     for (uint32_t c = lane; c < vdim; c += 32) q = fmaf(o[c], o[c], q);
-    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)vdim + eps);
-    for (uint32_t c = lane; c < vdim; c += 32) o[c] = o[c] * inv * wld(wts, (size_t)nw_off + c) * sigmoidf_(g[c]);
+    const float inv = out_scale / sqrtf(warp_sum(q) / (float)vdim + eps);
+    for (uint32_t c = lane; c < vdim; c += 32) o[c] = o[c] * inv * wld(wts, (size_t)nw_off + c) * (silu_gate ? g[c] * sigmoidf_(g[c]) : sigmoidf_(g[c]));
 }
 
 // ── ROUTE: one warp per token ────────────────────────────────────────────────────────────────────────────────────
@@ -1418,7 +1434,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (!fits(0, s.off[3], (M - 1) * drs + N) || !fits(1, s.off[2], (M - 1) * srs + K) || !wfits(2, s.off[0], N * K)) return fail("linear: extent");
             if (s.buf[3] != ZG_NO_BUF && !wfits(3, s.off[1], N)) return fail("linear: bias extent");
             if (s.buf[0] == s.buf[1]) return fail("linear: in place");
-            if (s.n[6] > 4) return fail("linear: activation");
+            if (s.n[6] > 5 || (s.n[6] == 5 && !(s.f[0] > 0.0f))) return fail("linear: activation");
             return true;
         }
         case ZG_OP_NORM: {
@@ -1465,11 +1481,13 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         }
         case ZG_OP_DELTA_RULE: {
             const size_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
-            if (!T || !H || !G || H % G || !dim || !vdim || zg_delta_row_slices((uint32_t)dim) > 32) return fail("delta_rule: shape");
-            if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || s.off[3] + H > s.n[6] || H * dim > s.n[7] || s.off[7] + H * vdim > s.n[8])
+            const size_t form = s.n[10], drs = s.n[11] ? s.n[11] : H * vdim;
+            if (!T || !H || !G || H % G || !dim || !vdim || zg_delta_row_slices((uint32_t)dim) > 32 || form > 7) return fail("delta_rule: shape");
+            if (s.n[12] + H * vdim > drs || ((form & 2) && !(s.f[3] > 0.0f))) return fail("delta_rule: form");
+            if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || (!(form & 1) && s.off[3] + H > s.n[6]) || H * dim > s.n[7] || s.off[7] + H * vdim > s.n[8])
                 return fail("delta_rule: columns");
-            if (!fits(0, 0, T * H * vdim) || !fits(1, 0, T * s.n[5]) || !fits(2, 0, T * s.n[6]) || !fits(3, 0, T * s.n[7]) || !fits(4, 0, T * s.n[8]) ||
-                !wfits(5, s.off[4], H) || !wfits(5, s.off[5], H * dim) || !wfits(5, s.off[6], vdim) || !have(6) || elems[s.buf[6]] < H * dim * vdim || !fits(7, 0, ZG_CTL_IDS))
+            if (!fits(0, 0, (T - 1) * drs + s.n[12] + H * vdim) || !fits(1, 0, T * s.n[5]) || (!(form & 1) && !fits(2, 0, T * s.n[6])) || !fits(3, 0, T * s.n[7]) || !fits(4, 0, T * s.n[8]) ||
+                (!(form & 2) && !wfits(5, s.off[4], H)) || !wfits(5, s.off[5], H * dim) || !wfits(5, s.off[6], vdim) || !have(6) || elems[s.buf[6]] < H * dim * vdim || !fits(7, 0, ZG_CTL_IDS))
                 return fail("delta_rule: extent");
             return true;
         }
@@ -1548,7 +1566,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             const bool has_bias = s.buf[3] != ZG_NO_BUF;
             if (scratch && zg_seq_op_scratch_elems(op, bufs))
                 return zg_dense_gemm_launch(wptr<bf16>(bufs, s.buf[2], s.off[0]), has_bias ? wptr<bf16>(bufs, s.buf[3], s.off[1]) : nullptr, src, dst, M, N, K,
-                                            s.n[3], s.n[4], scratch, st, s.n[6]);
+                                            s.n[3], s.n[4], scratch, st, s.n[6], s.f[0]);
             ZG_SEQ_WDT(s.n[5], {
                 const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
                 const WT* b = has_bias ? wptr<WT>(bufs, s.buf[3], s.off[1]) : nullptr;
@@ -1557,13 +1575,13 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                     const size_t xs_bytes = (size_t)M * K * sizeof(float);
                     const bool vec = K % V == 0 && (reinterpret_cast<size_t>(W) & 15) == 0 && xs_bytes <= 48 * 1024;
                     const dim3 grid((N + 7) / 8);
-                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
-                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
-                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
-                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
+                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
+                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
+                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
+                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
                 } else {
                     const dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
-                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6]);
+                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
                 }
             });
             ZG_SEQ_CHECK();
@@ -1661,31 +1679,43 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         }
         case ZG_OP_DELTA_RULE: {
             const uint32_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
+            const uint32_t form = s.n[10], dst_rs = s.n[11] ? s.n[11] : H * vdim;
+            const float inv_tau = (form & kDeltaSigmoidDecay) ? 1.0f / s.f[3] : 0.0f, out_scale = s.f[4] != 0.0f ? s.f[4] : 1.0f;
+            float* dst = bufs[s.buf[0]] + s.n[12];
+            const float* betab = (form & kDeltaPlain) ? nullptr : bufs[s.buf[2]];
             const uint32_t RS = zg_delta_row_slices(dim), cols = kDeltaThreads / RS;
             const size_t smem = ((size_t)3 * kDeltaTile * RS * kDeltaRows + kDeltaTile) * sizeof(float);
             const dim3 grid((vdim + cols - 1) / cols, H);
             if (scratch && T >= (uint32_t)kDeltaPrepMinTokens && dim <= (uint32_t)kWalkMaxDim) {
                 const uint32_t WS = delta_walk_slices(dim), dpad = WS * kWalkRows, wcols = kWalkThreads / WS;
                 const size_t walk_smem = (size_t)2 * kDeltaTile * (3 * dpad + 4) * sizeof(float);
-                ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_prepare<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, scratch, bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]],
-                                              wptr<WT>(bufs, s.buf[5], 0), T, H, G, dim, dpad, s.off[0], s.off[1], s.off[3], s.off[4], s.off[5], s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]));
+                ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_prepare<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, scratch, bufs[s.buf[1]], betab, bufs[s.buf[3]],
+                                              wptr<WT>(bufs, s.buf[5], 0), T, H, G, dim, dpad, s.off[0], s.off[1], s.off[3], s.off[4], s.off[5], s.n[5], s.n[6], s.n[7], s.f[1], s.f[2],
+                                              form, inv_tau));
                 ZG_SEQ_CHECK();
 #define ZG_WALK(RS_)                                                                                                                            \
     case RS_:                                                                                                                                   \
-        if (walk_smem > 48 * 1024) cudaFuncSetAttribute(k_delta_walk<RS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem);        \
-        launch_pdl(k_delta_walk<RS_>, dim3((vdim + wcols - 1) / wcols, H), dim3(kWalkThreads), walk_smem, st, bufs[s.buf[0]], bufs[s.buf[1]],   \
-                   scratch, bufs[s.buf[6]], bufs[s.buf[7]], T, H, dim, vdim, s.off[2], s.n[5]);                                                 \
+        if (form & kDeltaPlain) {                                                                                                               \
+            if (walk_smem > 48 * 1024) cudaFuncSetAttribute(k_delta_walk<RS_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem); \
+            launch_pdl(k_delta_walk<RS_, true>, dim3((vdim + wcols - 1) / wcols, H), dim3(kWalkThreads), walk_smem, st, dst, bufs[s.buf[1]],    \
+                       scratch, bufs[s.buf[6]], bufs[s.buf[7]], T, H, dim, vdim, s.off[2], s.n[5], dst_rs);                                     \
+        } else {                                                                                                                                \
+            if (walk_smem > 48 * 1024) cudaFuncSetAttribute(k_delta_walk<RS_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)walk_smem); \
+            launch_pdl(k_delta_walk<RS_, false>, dim3((vdim + wcols - 1) / wcols, H), dim3(kWalkThreads), walk_smem, st, dst, bufs[s.buf[1]],   \
+                       scratch, bufs[s.buf[6]], bufs[s.buf[7]], T, H, dim, vdim, s.off[2], s.n[5], dst_rs);                                     \
+        }                                                                                                                                       \
         break;
                 switch (WS) { ZG_WALK(1) ZG_WALK(2) ZG_WALK(4) ZG_WALK(8) ZG_WALK(16) default: ZG_WALK(32) }
 #undef ZG_WALK
             } else ZG_SEQ_WDT(s.n[9], {
                 if (smem > 48 * 1024) cudaFuncSetAttribute(k_delta_rule<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                launch_pdl(k_delta_rule<WT>, dim3(grid), dim3(kDeltaThreads), smem, st, bufs[s.buf[0]], bufs[s.buf[1]], bufs[s.buf[2]], bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
+                launch_pdl(k_delta_rule<WT>, dim3(grid), dim3(kDeltaThreads), smem, st, dst, bufs[s.buf[1]], betab, bufs[s.buf[3]], wptr<WT>(bufs, s.buf[5], 0), bufs[s.buf[6]],
                                                                   bufs[s.buf[7]], T, H, G, dim, vdim, RS, s.off[0], s.off[1], s.off[2], s.off[3], s.off[4], s.off[5],
-                                                                  s.n[5], s.n[6], s.n[7], s.f[1], s.f[2]);
+                                                                  s.n[5], s.n[6], s.n[7], s.f[1], s.f[2], form, inv_tau, dst_rs);
             });
             ZG_SEQ_CHECK();
-            ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_out<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, bufs[s.buf[0]], bufs[s.buf[4]] + s.off[7], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0]));
+            ZG_SEQ_WDT(s.n[9], launch_pdl(k_delta_out<WT>, dim3((T * H + 3) / 4), dim3(128), 0, st, dst, bufs[s.buf[4]] + s.off[7], wptr<WT>(bufs, s.buf[5], 0), T * H, H, vdim, s.n[8], s.off[6], s.f[0],
+                                                           dst_rs, (uint32_t)((form & kDeltaSiluGate) != 0), out_scale));
             ZG_SEQ_CHECK();
             return true;
         }

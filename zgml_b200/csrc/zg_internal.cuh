@@ -384,11 +384,11 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
 uint32_t zg_mix_op_writes(uint32_t tag);
 size_t zg_mix_op_scratch_elems(const ZgOp& op);
 bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st);
-// recops.cu : ZG_OP_SSM_SCAN .. ZG_OP_ACTIVATION, reached the same way
+// recops.cu : ZG_OP_SSM_SCAN .. ZG_OP_RG_LRU, reached the same way
 bool zg_rec_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* why, size_t why_n);
 uint32_t zg_rec_op_writes(uint32_t tag);
 size_t zg_rec_op_scratch_elems(const ZgOp& op);   // shared scratch of a long SSM_SCAN step: the states its segments reach and start from
 bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st);
 size_t zg_seq_op_operand_scratch(const ZgOp& op);   // f32 slots an op's own scratch operand needs (MOE_FFN)
 bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float* src, float* dst, uint32_t M, uint32_t N, uint32_t K,
-                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act = 0);   // act: 0 none, 1 + ACTIVATION kind
+                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act = 0, float act_p = 0.0f);   // act: 0 none, 1 + ACTIVATION kind

@@ -51,6 +51,14 @@ def _open_pepevik(be, path, dtype, n_slots, max_chunk, max_tokens):
     return SequenceSession(be, model, n_slots=n_slots, max_chunk=max_chunk, max_context=max_tokens or None)
 
 
+@register("Setirax")
+def _open_setirax(be, path, dtype, n_slots, max_chunk, max_tokens):
+    from .session import SequenceSession
+    from .setirax import SetiraxModel
+    model = SetiraxModel.load(be, path, dtype)
+    return SequenceSession(be, model, n_slots=n_slots, max_chunk=max_chunk, max_context=max_tokens or None)
+
+
 class LlamaServingSession:
     """The session surface over `DeviceLlamaSession` (one live request, one token per program execution: the reference's
     decode path).  Quantized GGUF weights run in f32 activations, so `dtype` only accepts "float32"-compatible requests."""

@@ -44,7 +44,7 @@ const ZgOp = extern struct {
         // extensions (tags 12 / 13): collectives of a row-sharded program; zgml's DeviceOp has no such variants yet
         allreduce: extern struct { buf: u32, offset: u32, n: u32 },
         allgather: extern struct { dst: u32, src: u32, n: u32, dst_offset: u32, src_offset: u32 },
-        seq: extern struct { buf: [8]u32, off: [8]u32, n: [10]u32, f: [4]f32 }, // sequence-model extensions (not emitted by zgml)
+        seq: extern struct { buf: [8]u32, off: [8]u32, n: [16]u32, f: [8]f32 }, // sequence-model extensions (not emitted by zgml)
     },
 };
 const ZgIO = extern struct { buf_idx: u32, offset: u32, host_ptr: ?*anyopaque, size: u32, _pad: u32 = 0 };
