@@ -148,13 +148,13 @@ typedef enum ZgOpTag {
  *                   7 gate (column of its row)
  *                   n 0 T 1 H 2 G 3 dim 4 vdim 5 qkv row stride 6 beta row stride 7 a row stride 8 gate row stride 9 wdt
  *                   10 form 11 dst row stride (0: H * vdim) 12 dst column
- *                   f 0 output-norm eps 1 unit-vector eps 2 q scale 3 decay temperature 4 output scale (0: 1)
+ *                   f 0 output-norm eps 1 unit-vector eps 2 q scale 3 decay temperature 4 output scale
  *                   Form bits (n10), all clear for the rule above.  Bit 0, plain accumulation (gated linear attention): no
  *                   unit vectors (q is only scaled by f2) and no correction by what the state already holds, u = v:
  *                   S <- g * S + k v^T, o = S^T q; buf 2 is not read.  Bit 1: the decay is g = sigmoid(a + dt_bias)^(1 / f3),
  *                   evaluated as exp(-softplus(-(a + dt_bias)) / f3); A_log is not read.  Bit 2: the output gate is
- *                   silu(gate) instead of sigmoid(gate).  The result is multiplied by f4 and may land in columns of a wider
- *                   row (n11, n12), beside another mixer's heads.
+ *                   silu(gate) instead of sigmoid(gate).  Bit 3: the result is multiplied by f4.  It may land in columns of a
+ *                   wider row (n11, n12), beside another mixer's heads.
  * ROUTE             mode 0: s = softmax(logits) over all NE outputs; the `top` largest of s + correction are chosen (ties:
  *                   lowest index); dst[t, c] = {index as int32 bits, s[index]} (weights not renormalised)
  *                   mode 1: z = logits + correction (a bias); the `top` largest z are chosen (ties: lowest index) and weighted
@@ -203,13 +203,13 @@ typedef enum ZgOpTag {
  *                   With f1 > 0 the scaled score is capped smoothly first: f1 * tanh(s / f1).  With buf 6 a learned SINK per
  *                   (head, map) joins the softmax: exp(sink) is added to the denominator alone; it has no key and no value, is
  *                   neither scaled nor capped, and counts once (a weight operand: element off 7 of buf 6, type n12).  The
- *                   result is multiplied by f2 (0: 1) and may land in columns of a wider row (n10 row stride, 0: H * maps * dv;
+ *                   result is multiplied by f2 where n13 = 1 and may land in columns of a wider row (n10 row stride, 0: H * maps * dv;
  *                   n11 first column), beside another mixer's heads.
  *                   buf 0 dst [T, H * maps, dv] 1 q 2 key cache 3 value cache 4 ctl 5 score table 6 sinks
  *                   off 0 q column 1 key column 2 value column (inside a cache row) 3 mask kind 4 mask size 5 weights 6 table row length
  *                   7 sinks
  *                   n 0 T 1 H 2 G 3 maps 4 dk 5 dv 6 q row stride 7 key row width 8 value row width 9 R 10 dst row stride
- *                   11 dst column 12 wdt of the sinks | f 0 score scale 1 score cap 2 output scale
+ *                   11 dst column 12 wdt of the sinks 13 output scale given | f 0 score scale 1 score cap 2 output scale
  * MAP_COMBINE       differential attention's combination of two maps: o = a[.., 0, :] - f0 * a[.., 1, :], then
  *                   o / sqrt(mean(o^2) + f1) * f2 per (token, head)
  *                   buf 0 dst [rows, dv] 1 src [rows, 2, dv] | n 0 rows 1 dv | f 0 lambda 1 eps 2 output scale

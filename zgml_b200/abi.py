@@ -27,7 +27,7 @@ OP_END = 37
 MASK_CAUSAL, MASK_WINDOW, MASK_BLOCK = 0, 1, 2
 NORM_LAYER, NORM_RMS, NORM_UNIT_OFFSET, NORM_GAIN = 0, 1, 2, 4
 NORM_DYNAMIC_TANH, NORM_NONE = 8, 16       # tanh(alpha x) w + b (bias and alpha follow w); the row itself: no statistics either way
-DELTA_PLAIN, DELTA_SIGMOID_DECAY, DELTA_SILU_GATE = 1, 2, 4     # forms of DELTA_RULE (n10)
+DELTA_PLAIN, DELTA_SIGMOID_DECAY, DELTA_SILU_GATE, DELTA_OUT_SCALE = 1, 2, 4, 8     # forms of DELTA_RULE (n10)
 WEIGHTS_SOFTMAX, WEIGHTS_SIGMOID = 0, 1    # CACHED_ATTENTION: normalised over the visible keys, or sigmoid(score) of each
 ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "relu": 3, "softcap": 4}     # "softcap": p * tanh(z / p), p the op's activation parameter
 NO_BUF = 0xFFFFFFFF

@@ -267,15 +267,16 @@ class DeviceOp:
     @staticmethod
     def delta_rule(dst, qkv, beta, a, gate, w, state, ctl, q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off,
                    T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, norm_eps, unit_eps, q_scale, gate_off=0, plain=False, decay_tau=None,
-                   silu_gate=False, out_scale=0.0, dst_rs=0, dst_col=0):
+                   silu_gate=False, out_scale=None, dst_rs=0, dst_col=0):
         """`plain`: no unit vectors and no correction by the state (S <- g S + k v^T: gated linear attention; `beta` may be None).
         `decay_tau`: the decay is sigmoid(a + dt_bias)^(1 / tau) instead of exp(-exp(A_log) softplus(a + dt_bias)).  `silu_gate`: the
         output gate is silu instead of sigmoid.  `out_scale` multiplies the result, which may land at column `dst_col` of rows
         `dst_rs` wide."""
-        form = (abi.DELTA_PLAIN if plain else 0) | (abi.DELTA_SIGMOID_DECAY if decay_tau is not None else 0) | (abi.DELTA_SILU_GATE if silu_gate else 0)
+        form = (abi.DELTA_PLAIN if plain else 0) | (abi.DELTA_SIGMOID_DECAY if decay_tau is not None else 0) | (abi.DELTA_SILU_GATE if silu_gate else 0) | \
+            (abi.DELTA_OUT_SCALE if out_scale is not None else 0)
         return DeviceOp._seq(abi.OP_DELTA_RULE, [dst, qkv, beta, a, gate, w, state, ctl],
                              [q_off, k_off, v_off, beta_off, a_log_off, dt_bias_off, norm_off, gate_off],
-                             [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, form, dst_rs, dst_col], [norm_eps, unit_eps, q_scale, decay_tau or 0.0, out_scale])
+                             [T, H, G, dim, vdim, qkv_rs, beta_rs, a_rs, gate_rs, wdt, form, dst_rs, dst_col], [norm_eps, unit_eps, q_scale, decay_tau or 0.0, out_scale or 0.0])
 
     @staticmethod
     def route(dst, logits, w, corr_off, T, n_outputs, top, wdt, logits_off=0, logits_rs=0, mode="corrected_softmax", groups=0, groups_kept=0):
@@ -318,7 +319,7 @@ class DeviceOp:
     @staticmethod
     def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,
                          mask="causal", mask_size=0, weights="softmax", score_table=None, table_len=0, softcap=0.0, sink=None, sink_off=0, sink_wdt=0,
-                         out_scale=0.0, dst_rs=0, dst_col=0):
+                         out_scale=None, dst_rs=0, dst_col=0):
         """`score_table`: an f32 buffer [H * maps, table_len] added to the scaled scores by distance; `weights` "sigmoid": every
         visible key weighs sigmoid(score), not normalised over the keys.  `softcap` > 0: the scaled score passes cap * tanh(s / cap).
         `sink`: a weight buffer with one learned score per (head, map) at `sink_off` whose exponential joins the softmax's denominator.
@@ -326,7 +327,7 @@ class DeviceOp:
         kinds = {"causal": abi.MASK_CAUSAL, "window": abi.MASK_WINDOW, "block": abi.MASK_BLOCK}
         return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl, score_table, sink],
                              [q_col, k_col, v_col, kinds[mask], mask_size, {"softmax": abi.WEIGHTS_SOFTMAX, "sigmoid": abi.WEIGHTS_SIGMOID}[weights], table_len, sink_off],
-                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, dst_rs, dst_col, sink_wdt], [scale, softcap, out_scale])
+                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, dst_rs, dst_col, sink_wdt, int(out_scale is not None)], [scale, softcap, out_scale or 0.0])
 
     @staticmethod
     def map_combine(dst, src, rows, dv, lam, eps, out_scale):

@@ -836,7 +836,7 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (R < T) return fail("cached_attention: cache rows");   // the caller sizes R for what the mask reaches and bounds the positions
             if (s.off[0] + H * maps * dk > qrs || s.off[1] + G * maps * dk > kw || s.off[2] + G * dv > vw) return fail("cached_attention: columns");
             const size_t drs = s.n[10] ? s.n[10] : H * maps * dv;
-            if (s.n[11] + H * maps * dv > drs || s.f[1] < 0.0f) return fail("cached_attention: destination columns or cap");
+            if (s.n[11] + H * maps * dv > drs || s.f[1] < 0.0f || s.n[13] > 1) return fail("cached_attention: destination columns, cap or output scale");
             if (s.buf[6] != ZG_NO_BUF && (s.off[5] || !wfits(6, s.n[12], s.off[7], H * maps))) return fail("cached_attention: sinks");
             if (!fits(0, 0, (T - 1) * drs + s.n[11] + H * maps * dv) || !fits(1, 0, (T - 1) * qrs + s.off[0] + H * maps * dk) || !have(2) || elems[s.buf[2]] < R * kw || !have(3) ||
                 elems[s.buf[3]] < R * vw || !fits(4, 0, ZG_CTL_IDS))
@@ -931,7 +931,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.T = s.n[0]; a.H = s.n[1]; a.G = s.n[2]; a.maps = s.n[3]; a.dk = s.n[4]; a.dv = s.n[5]; a.q_rs = s.n[6]; a.q_off = s.off[0];
             a.kw = s.n[7]; a.k_off = s.off[1]; a.vw = s.n[8]; a.v_off = s.off[2]; a.R = s.n[9]; a.kind = s.off[3]; a.size = s.off[4]; a.scale = s.f[0];
             a.tab = s.buf[5] != ZG_NO_BUF ? bufs[s.buf[5]] : nullptr; a.tab_rs = s.off[6]; a.wkind = s.off[5];
-            a.cap = s.f[1]; a.out_scale = s.f[2] != 0.0f ? s.f[2] : 1.0f; a.dst_rs = s.n[10] ? s.n[10] : a.H * a.maps * a.dv; a.dst += s.n[11];
+            a.cap = s.f[1]; a.out_scale = s.n[13] ? s.f[2] : 1.0f; a.dst_rs = s.n[10] ? s.n[10] : a.H * a.maps * a.dv; a.dst += s.n[11];
             a.sink = nullptr; a.sink_bf16 = s.n[12] == ZG_W_BF16;
             if (s.buf[6] != ZG_NO_BUF) a.sink = a.sink_bf16 ? (const void*)wptr<bf16>(bufs, s.buf[6], s.off[7]) : (const void*)wptr<float>(bufs, s.buf[6], s.off[7]);
             const bool aligned = ca_aligned(s) && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;

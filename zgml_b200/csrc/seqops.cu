@@ -845,8 +845,8 @@ __global__ void k_conv_advance(float* __restrict__ state, const float* __restric
 // prepared by the whole CTA at once, then the tokens are walked without further barriers.
 constexpr int kDeltaRows = 16, kDeltaTile = 16, kDeltaThreads = 128;
 // forms of the rule (op parameter n10): plain accumulation without unit vectors and correction (gated linear attention), the
-// decay as a tempered sigmoid, a SiLU output gate
-constexpr uint32_t kDeltaPlain = 1, kDeltaSigmoidDecay = 2, kDeltaSiluGate = 4;
+// decay as a tempered sigmoid, a SiLU output gate, an output scale
+constexpr uint32_t kDeltaPlain = 1, kDeltaSigmoidDecay = 2, kDeltaSiluGate = 4, kDeltaOutScale = 8;
 // decay of one key channel from its logit z (the bias is already added): exp(-exp(A) softplus(z)), or sigmoid(z)^(1 / tau) =
 // exp(-softplus(-z) / tau)
 __device__ __forceinline__ float delta_decay(float z, float Ah, uint32_t form, float inv_tau) {
@@ -1482,7 +1482,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
         case ZG_OP_DELTA_RULE: {
             const size_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
             const size_t form = s.n[10], drs = s.n[11] ? s.n[11] : H * vdim;
-            if (!T || !H || !G || H % G || !dim || !vdim || zg_delta_row_slices((uint32_t)dim) > 32 || form > 7) return fail("delta_rule: shape");
+            if (!T || !H || !G || H % G || !dim || !vdim || zg_delta_row_slices((uint32_t)dim) > 32 || form > 15) return fail("delta_rule: shape");
             if (s.n[12] + H * vdim > drs || ((form & 2) && !(s.f[3] > 0.0f))) return fail("delta_rule: form");
             if (s.off[0] + G * dim > s.n[5] || s.off[1] + G * dim > s.n[5] || s.off[2] + H * vdim > s.n[5] || (!(form & 1) && s.off[3] + H > s.n[6]) || H * dim > s.n[7] || s.off[7] + H * vdim > s.n[8])
                 return fail("delta_rule: columns");
@@ -1680,7 +1680,7 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
         case ZG_OP_DELTA_RULE: {
             const uint32_t T = s.n[0], H = s.n[1], G = s.n[2], dim = s.n[3], vdim = s.n[4];
             const uint32_t form = s.n[10], dst_rs = s.n[11] ? s.n[11] : H * vdim;
-            const float inv_tau = (form & kDeltaSigmoidDecay) ? 1.0f / s.f[3] : 0.0f, out_scale = s.f[4] != 0.0f ? s.f[4] : 1.0f;
+            const float inv_tau = (form & kDeltaSigmoidDecay) ? 1.0f / s.f[3] : 0.0f, out_scale = (form & kDeltaOutScale) ? s.f[4] : 1.0f;
             float* dst = bufs[s.buf[0]] + s.n[12];
             const float* betab = (form & kDeltaPlain) ? nullptr : bufs[s.buf[2]];
             const uint32_t RS = zg_delta_row_slices(dim), cols = kDeltaThreads / RS;
