@@ -773,10 +773,10 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the 2-layer oracle comparison")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--arch", default="", choices=["", "lududra", "vemepel", "pepevik"],
+    ap.add_argument("--arch", default="", choices=["", "lududra", "vemepel", "pepevik", "setirax"],
                     help="side bench instead of the default workload: prefill / decode throughput of that design next to the framework's closest "
-                         "model at equal layer sizes (lududra: a LLaMA; vemepel, pepevik: Lududra)")
-    ap.add_argument("--arms", default="", help="--arch pepevik: comma-separated arms to run (default: both)")
+                         "model at equal layer sizes (lududra: a LLaMA; vemepel, pepevik: Lududra; setirax: Pepevik)")
+    ap.add_argument("--arms", default="", help="--arch pepevik, setirax: comma-separated arms to run (default: both)")
     ap.add_argument("--sizes", default="", help="--arch: comma-separated size names (default: all)")
     ap.add_argument("--prefill-tokens", type=int, default=1024, help="--arch: tokens of the timed prefill chunk")
     ap.add_argument("--context", type=int, default=1024, help="--arch: tokens in the sequence before the timed decode steps")

@@ -406,3 +406,82 @@ class SetiraxModel:
         for b in list(self.buffers.values()) + list(self._freqs.values()):
             b.free()
         self.buffers, self._freqs = {}, {}
+
+
+def synthetic_config(width: int, n_layers: int, heads: int, kv_heads: int, dim: int, ff: int, vocab: int, window: int = 1024, kv_rank: int = 512,
+                     gla_heads: Optional[int] = None, lru_width: Optional[int] = None, lru_blocks: Optional[int] = None, conv: int = 4) -> dict:
+    """config.json contents of a random-init model: layers cycle latent attention, the pair and the recurrent block; every layer
+    but the recurrent ones has a dense feed-forward."""
+    layers = []
+    for i in range(n_layers):
+        kind = MIXERS[i % 3]
+        if kind == "latent_attention":
+            mixer = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": kv_rank, "mask": {"size": window}, "scale": dim ** -0.5}
+        elif kind == "parallel":
+            left = {"conv": conv, "dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": window}, "scale": 8.0 / dim, "softcap": 20.0, "vdim": dim,
+                    "rot": {"base": 10000.0, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            right = {"dim": dim, "heads": gla_heads or max(1, heads // 2), "tau": 16.0, "vdim": dim}
+            mixer = {"left": left, "left_scale": 0.5, "right": right, "right_scale": 0.5}
+        else:
+            mixer = {"blocks": lru_blocks or heads, "conv": conv, "width": lru_width or width}
+        layers.append({"type": kind, "mixer": mixer, "mlp": None if kind == "rglru" else {"kind": "dense", "ff": ff}})
+    return {"architecture": ARCHITECTURE, "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers}
+
+
+def synthetic_tensors(cfg: dict, seed: int = 0, decay_rank: int = 64):
+    """Accessor name -> random f32 tensor of the shape the configuration implies (benchmarks and smoke runs; values are scaled like a
+    trained model's so that activations stay O(1))."""
+    D = cfg["width"]
+
+    def shape_of(name):
+        if name == "embed":
+            return (cfg["vocab"], D)
+        if name == "final.norm":
+            return (D,)
+        layer, rest = name.split(".", 1)
+        L = cfg["layers"][int(layer[1:])]
+        m = L["mixer"]
+        if rest in ("norm1", "norm2"):
+            return (D,)
+        if rest.startswith("mlp."):
+            ff = L["mlp"]["ff"]
+            return {"up": (ff, D), "up.b": (ff,), "down": (D, ff), "down.b": (D,)}[rest[4:]]
+        t = rest[len("mix."):]
+        if L["type"] == "latent_attention":
+            H, d, dv, rk = m["heads"], m["dim"], m["vdim"], m["kv_rank"]
+            return {"q": (H * d, D), "dkv": (rk, D), "dkv.norm": (rk,), "uk": (H * d, rk), "uv": (H * dv, rk), "sink": (H,), "o": (D, H * dv)}[t]
+        if L["type"] == "parallel":
+            l, r = m["left"], m["right"]
+            H, G, d, dv, taps = l["heads"], l["kv_heads"], l["dim"], l["vdim"], l["conv"]
+            Hr, dr, vr = r["heads"], r["dim"], r["vdim"]
+            return {"left.q": (H * d, D), "left.k": (G * d, D), "left.v": (G * dv, D), "left.q.conv": (H * d, taps), "left.k.conv": (G * d, taps), "left.v.conv": (G * dv, taps),
+                    "left.o": (D, H * dv), "right.q": (Hr * dr, D), "right.k": (Hr * dr, D), "right.v": (Hr * vr, D), "right.g": (Hr * vr, D), "right.a1": (decay_rank, D),
+                    "right.a2": (Hr * dr, decay_rank), "right.a2.b": (Hr * dr,), "right.norm": (vr,), "right.o": (D, Hr * vr)}[t]
+        W, B, taps = m["width"], m["blocks"], m["conv"]
+        bw = W // B
+        return {"y": (W, D), "y.b": (W,), "x": (W, D), "x.b": (W,), "conv": (W, taps), "conv.b": (W,), "ra": (B, bw, bw), "ra.b": (B, bw), "ri": (B, bw, bw), "ri.b": (B, bw),
+                "lam": (W,), "o": (D, W)}[t]
+
+    def get(name):
+        import zlib
+        shp = shape_of(name)
+        r = np.random.default_rng([seed, zlib.crc32(name.encode())])
+        last = name.rsplit(".", 1)[-1]
+        if last in ("norm", "norm1", "norm2"):
+            return np.ones(shp, np.float32)
+        if last == "conv":
+            a = (r.random(shp, dtype=np.float32) - 0.5) * 0.5
+            a[:, -1] += 1.0
+            return a
+        if name.endswith("a2.b"):
+            return (2.0 + r.random(shp, dtype=np.float32)).astype(np.float32)
+        if last == "lam":
+            return (-3.0 + 2.0 * r.random(shp, dtype=np.float32)).astype(np.float32)
+        if last in ("b", "sink"):
+            return (r.random(shp, dtype=np.float32) * 0.2).astype(np.float32)
+        a = r.random(shp, dtype=np.float32)
+        a -= 0.5
+        a *= np.float32(np.sqrt(12.0 / shp[-1]))
+        return a
+
+    return get
