@@ -187,9 +187,13 @@ typedef enum ZgOpTag {
  *                   normed columns are normed in groups of n9 (key heads), every group with the same weight of n9 values.
  *                   With off5 > 0 the same launch norms off5 QUERY heads of n9 values in place in the source rows (column off 3,
  *                   weight at off 4), times the temperature 1 + f2 * ln(floor((p + 1) / off6) + 1) (off6 = 0: none): HEAD_NORM fused.
- *                   buf 0 cache 1 src 2 ctl 3 norm weight | off 0 src column 1 cache column 2 norm weight 3 query column 4 query weight
- *                   5 query heads 6 temperature period
- *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout 9 norm group
+ *                   With n10 > 0 (and n9 > 0) every normed group — key heads, and the query heads of off5 — is first turned by
+ *                   the token's rotary position on its first n10 values (layout n8; frequencies base^(-2i / n10) from f1, or
+ *                   from the f32 table buf 4 at element off 7, as ROTARY takes it), and the root mean square is that of the
+ *                   turned vector: ROTARY fused, for designs that norm after the rotation.
+ *                   buf 0 cache 1 src 2 ctl 3 norm weight 4 frequency table | off 0 src column 1 cache column 2 norm weight 3 query column
+ *                   4 query weight 5 query heads 6 temperature period 7 frequency table offset
+ *                   n 0 T 1 columns 2 src row stride 3 width 4 R 5 normed 6 rot 7 wdt 8 rotary layout 9 norm group 10 rotary inside the groups
  *                   f 0 eps 1 rotary base 2 temperature coefficient
  * CACHED_ATTENTION  softmax attention of the step's queries over cached keys and values.  A query row holds H * maps vectors
  *                   of dk (head h, map m at (h * maps + m) * dk); a key row G * maps vectors of dk; a value row G vectors of

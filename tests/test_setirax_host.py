@@ -83,8 +83,10 @@ def test_state_and_lowering_shape(fake_device):
         tags = [op.tag for op in ops]
         assert tags[0] == abi.OP_EMBED and lp.logits_rows == rows and (lp.buf_logits is None) == (head == "none")
         assert tags.count(abi.OP_CACHED_ATTENTION) == 4 and tags.count(abi.OP_CACHE_APPEND) == 4 and tags.count(abi.OP_HEAD_LINEAR) == 2 * 2 + 2
-        assert tags.count(abi.OP_DELTA_RULE) == 2 and tags.count(abi.OP_ROTARY) == 2 and tags.count(abi.OP_RG_LRU) == 2 and tags.count(abi.OP_CAUSAL_CONV) == 2 + 2
+        assert tags.count(abi.OP_DELTA_RULE) == 2 and tags.count(abi.OP_ROTARY) == 0 and tags.count(abi.OP_RG_LRU) == 2 and tags.count(abi.OP_CAUSAL_CONV) == 2 + 2
         assert tags.count(abi.OP_ACTIVATION) == 0 and sum(op.tag == abi.OP_LINEAR and op.u.seq.n[6] == abi.ACTIVATIONS["relu2"] + 1 for op in ops) == 5
+        app = [op for op in ops if op.tag == abi.OP_CACHE_APPEND]
+        assert [op.u.seq.n[10] for op in app] == [0, 6, 0, 6] and app[1].u.seq.buf[4] == app[3].u.seq.buf[4] != abi.NO_BUF      # rotary rides in the append, from one table
         att = [op for op in ops if op.tag == abi.OP_CACHED_ATTENTION]
         assert [op.u.seq.buf[6] != abi.NO_BUF for op in att] == [True, False, True, False]       # sinks on the latent layers only
         assert [op.u.seq.f[1] for op in att] == [0.0, 5.0, 0.0, 5.0] and all(op.u.seq.off[3] == abi.MASK_WINDOW for op in att)

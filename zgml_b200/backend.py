@@ -309,12 +309,16 @@ class DeviceOp:
 
     @staticmethod
     def cache_append(cache, src, ctl, src_col, cache_col, T, cols, src_rs, width, rows, norm_w=None, norm_off=0, normed=0, eps=0.0, wdt=0,
-                     rot=0, rot_base=0.0, rot_layout="pairs", norm_group=0, q_heads=0, q_col=0, q_norm_off=0, temp_coef=0.0, temp_every=0):
+                     rot=0, rot_base=0.0, rot_layout="pairs", norm_group=0, q_heads=0, q_col=0, q_norm_off=0, temp_coef=0.0, temp_every=0, head_rot=0,
+                     freqs=None, freqs_off=0):
         """`norm_group` > 0: the normed columns are normed in groups of that many (key heads) sharing one weight of that size.
         `q_heads` > 0: that many query heads of norm_group values at column q_col of the source rows are normed in place by the same
-        launch (weight at q_norm_off of norm_w's arena), times the position-dependent temperature of HEAD_NORM."""
-        return DeviceOp._seq(abi.OP_CACHE_APPEND, [cache, src, ctl, norm_w if normed else None], [src_col, cache_col, norm_off, q_col, q_norm_off, q_heads, temp_every],
-                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout], norm_group], [eps, rot_base, temp_coef])
+        launch (weight at q_norm_off of norm_w's arena), times the position-dependent temperature of HEAD_NORM.
+        `head_rot` > 0: every normed group (key and query heads) is first turned by the token's rotary position on its first head_rot
+        values (`rot_layout`; frequencies from `rot_base`, or from the f32 table `freqs` at element `freqs_off`), then normed."""
+        return DeviceOp._seq(abi.OP_CACHE_APPEND, [cache, src, ctl, norm_w if normed else None, freqs if head_rot else None],
+                             [src_col, cache_col, norm_off, q_col, q_norm_off, q_heads, temp_every, freqs_off],
+                             [T, cols, src_rs, width, rows, normed, rot, wdt, {"pairs": 0, "halves": 1}[rot_layout], norm_group, head_rot], [eps, rot_base, temp_coef])
 
     @staticmethod
     def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,

@@ -69,13 +69,49 @@ __global__ void k_rotary(float* x, const float* src, const float* __restrict__ c
 template <typename WT>
 __global__ void k_cache_append(float* __restrict__ cache, const float* __restrict__ src, const float* __restrict__ ctl, const WT* __restrict__ nw_,
                                uint32_t cols, uint32_t src_rs, uint32_t width, uint32_t R, uint32_t normed, uint32_t rot, uint32_t layout, float eps,
-                               float base, uint32_t norm_group, float* qsrc, const WT* __restrict__ qw, uint32_t q_heads, uint32_t temp_every, float temp_coef) {
+                               float base, uint32_t norm_group, float* qsrc, const WT* __restrict__ qw, uint32_t q_heads, uint32_t temp_every, float temp_coef,
+                               uint32_t hrot, const float* __restrict__ freqs) {
     pdl_enter();
     __shared__ float sh[32];
+    extern __shared__ float cs_sn[];                   // head rotary: cosine | sine of the token's hrot / 2 angles, shared by all heads
     const uint32_t t = blockIdx.x;
     const uint32_t pos = (uint32_t)ctl_word(ctl, ZG_CTL_POS) + t, slot = (uint32_t)ctl_word(ctl, ZG_CTL_SLOT);
     float* row = cache + ((size_t)slot * R + pos % R) * width;
     const float* s = src + (size_t)t * src_rs;
+    if (hrot) {
+        // Every key head (and query head) is first turned by the token's position on its first hrot values, then divided by the
+        // root mean square of the TURNED vector and weighted: rotary and norm of a head in one pass over it.  One warp per head;
+        // a lane turns whole pairs, so turning in place (the query heads) has no hazard between lanes.
+        const uint32_t hh = hrot / 2;
+        for (uint32_t i = threadIdx.x; i < hh; i += blockDim.x) {
+            float sn, cs;
+            if (freqs) sincosf((float)pos * freqs[i], &sn, &cs); else rotary_angle(pos, i, hrot, base, sn, cs);
+            cs_sn[i] = cs; cs_sn[hh + i] = sn;
+        }
+        __syncthreads();
+        const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+        const uint32_t n_key = normed / norm_group;
+        const float temp = temp_every ? fmaf(temp_coef, logf((float)((pos + 1) / temp_every) + 1.0f), 1.0f) : 1.0f;
+        for (uint32_t hd = warp; hd < n_key + q_heads; hd += nw) {
+            const bool key = hd < n_key;
+            const float* v = key ? s + (size_t)hd * norm_group : qsrc + (size_t)t * src_rs + (size_t)(hd - n_key) * norm_group;
+            float* d = key ? row + (size_t)hd * norm_group : qsrc + (size_t)t * src_rs + (size_t)(hd - n_key) * norm_group;
+            const WT* w = key ? nw_ : qw;
+            float q = 0.0f;
+            for (uint32_t i = lane; i < hh; i += 32) {
+                const uint32_t a = layout == 0 ? 2 * i : i, b = layout == 0 ? 2 * i + 1 : i + hh;
+                const float u = v[a], x = v[b], ru = u * cs_sn[i] - x * cs_sn[hh + i], rx = x * cs_sn[i] + u * cs_sn[hh + i];
+                d[a] = ru; d[b] = rx;
+                q = fmaf(ru, ru, fmaf(rx, rx, q));
+            }
+            for (uint32_t c = hrot + lane; c < norm_group; c += 32) { const float x = v[c]; d[c] = x; q = fmaf(x, x, q); }
+            const float mult = (key ? 1.0f : temp) / sqrtf(warp_sum(q) / (float)norm_group + eps);
+            __syncwarp();
+            for (uint32_t c = lane; c < norm_group; c += 32) d[c] = d[c] * mult * wld(w, c);
+        }
+        for (uint32_t c = normed + rot + threadIdx.x; c < cols; c += blockDim.x) row[c] = s[c];
+        return;
+    }
     if (normed && norm_group) {                        // key heads: every group of norm_group columns by its own root mean square, one warp each
         const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
         for (uint32_t g0 = warp * norm_group; g0 < normed; g0 += nw * norm_group) {
@@ -822,6 +858,10 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (normed && s.n[9] && normed % s.n[9]) return fail("cache_append: norm groups");
             if (normed && !wfits(3, s.n[7], s.off[2], s.n[9] ? s.n[9] : normed)) return fail("cache_append: norm weight");
             if (rot && !(s.f[1] > 0.0f)) return fail("cache_append: rotary base");
+            if (s.n[10]) {     // rotary inside every normed head, before its norm
+                if (!normed || !s.n[9] || rot || s.n[10] % 2 || s.n[10] > s.n[9]) return fail("cache_append: head rotary");
+                if (s.buf[4] != ZG_NO_BUF ? !fits(4, s.off[7], s.n[10] / 2) : !(s.f[1] > 0.0f)) return fail("cache_append: head rotary frequencies");
+            }
             if (s.off[5]) {    // query heads normed in place in the source rows
                 const size_t qh = s.off[5], hd = s.n[9];
                 if (!normed || !hd || s.off[3] + qh * hd > srs || !fits(1, 0, (T - 1) * srs + s.off[3] + qh * hd) || !wfits(3, s.n[7], s.off[4], hd)) return fail("cache_append: query heads");
@@ -920,9 +960,10 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             return true;
         }
         case ZG_OP_CACHE_APPEND:
-            ZG_SEQ_WDT(s.n[5] ? s.n[7] : ZG_W_F32, launch_pdl(k_cache_append<WT>, dim3(s.n[0]), dim3(s.off[5] ? 256 : 128), 0, st, bufs[s.buf[0]] + s.off[1], bufs[s.buf[1]] + s.off[0], bufs[s.buf[2]],
+            ZG_SEQ_WDT(s.n[5] ? s.n[7] : ZG_W_F32, launch_pdl(k_cache_append<WT>, dim3(s.n[0]), dim3(s.off[5] ? 256 : 128), (size_t)s.n[10] * sizeof(float), st, bufs[s.buf[0]] + s.off[1], bufs[s.buf[1]] + s.off[0], bufs[s.buf[2]],
                                                              s.n[5] ? wptr<WT>(bufs, s.buf[3], s.off[2]) : nullptr, s.n[1], s.n[2], s.n[3], s.n[4], s.n[5], s.n[6], s.n[8], s.f[0], s.f[1], s.n[9],
-                                                             s.off[5] ? bufs[s.buf[1]] + s.off[3] : nullptr, s.off[5] ? wptr<WT>(bufs, s.buf[3], s.off[4]) : nullptr, s.off[5], s.off[6], s.f[2]));
+                                                             s.off[5] ? bufs[s.buf[1]] + s.off[3] : nullptr, s.off[5] ? wptr<WT>(bufs, s.buf[3], s.off[4]) : nullptr, s.off[5], s.off[6], s.f[2],
+                                                             s.n[10], s.n[10] && s.buf[4] != ZG_NO_BUF ? (const float*)(bufs[s.buf[4]] + s.off[7]) : (const float*)nullptr));
             ZG_SEQ_CHECK();
             return true;
         case ZG_OP_CACHED_ATTENTION: {

@@ -20,9 +20,9 @@ latent      [q | dkv] = W x in ONE matmul; CACHE_APPEND norms the latent on its 
             q' = W_uk^T q per head (HEAD_LINEAR), CACHED_ATTENTION of q' over the latent itself (one key head that is also the
             value, window mask, sinks), then W_uv per head (HEAD_LINEAR) and W_o.  Scores (W_uk^T q) . c = q . (W_uk c) are the
             same numbers in another order of summation; nothing per head is cached.
-pair        [q | k | v | q' | k' | v' | g | a1] = W x in ONE matmul for both branches.  Left: CAUSAL_CONV over q | k | v, ROTARY
-            over the query and key heads from a frequency table evaluated at load, CACHE_APPEND (unit RMS per key head into the ring,
-            values copied, query heads normed in place), CACHED_ATTENTION (cap, window) writing left_scale * heads into the left
+pair        [q | k | v | q' | k' | v' | g | a1] = W x in ONE matmul for both branches.  Left: CAUSAL_CONV over q | k | v, CACHE_APPEND
+            (every key head turned by its rotary position — frequencies from a table evaluated at load — then brought to unit RMS on
+            its way into the ring, values copied, query heads turned and normed in place), CACHED_ATTENTION (cap, window) writing left_scale * heads into the left
             columns of a shared row.  Right: the decay logits' second stage (LINEAR), DELTA_RULE in its plain form (no unit
             vectors, no correction; tempered-sigmoid decay; SiLU gate) writing right_scale * heads into the right columns.  ONE
             matmul over the shared row with [W_o left | W_o right] is the scaled sum of the two branches.
@@ -347,14 +347,14 @@ class SetiraxModel:
                 else:
                     qkv, qrs = proj, ni
                 rot = l.get("rot")
-                if rot:     # query and key heads lie side by side and share the head size: one launch turns both
-                    ops.append(DeviceOp.rotary(qkv, ctl, 0, T, H + G, dim, qrs, rot["dims"], rot["base"], layout="halves", freqs=ext(self._freqs[owner])))
                 cache = pool.buffers[f"l{i}.kv"]
                 cw = G * (dim + vdim)
                 R = cache.elems // (slots * cw)
-                # one launch: unit RMS per key head on its way into the ring, values copied, unit RMS per query head in place
+                # one launch: every key head turned by its position, brought to unit RMS and written into the ring, values copied, every
+                # query head turned and brought to unit RMS in place
                 ops.append(DeviceOp.cache_append(ext(cache), qkv, ctl, H * dim, 0, T, cw, qrs, cw, R, norm_w=wb, norm_off=A.off["unit"], normed=G * dim, eps=eps, wdt=wdt,
-                                                 norm_group=dim, q_heads=H, q_col=0, q_norm_off=A.off["unit"]))
+                                                 norm_group=dim, q_heads=H, q_col=0, q_norm_off=A.off["unit"], rot_layout="halves", head_rot=rot["dims"] if rot else 0,
+                                                 rot_base=rot["base"] if rot else 0.0, freqs=ext(self._freqs[owner]) if rot else None))
                 mw = meta["mix"]
                 mix = scratch("mix", T * mw)
                 ops.append(DeviceOp.cached_attention(mix, qkv, ext(cache), ext(cache), ctl, 0, 0, G * dim, T, H, G, 1, dim, vdim, qrs, cw, cw, R, l["scale"],
