@@ -98,7 +98,8 @@ def test_state_and_lowering_shape(fake_device):
         assert abs(att[1].u.seq.f[2] - 0.7) < 1e-6 and abs(rule[0].u.seq.f[4] - 1.3) < 1e-6
         # the norm sits on every sublayer's result and carries the residual; nothing is normed before a sublayer
         norms = [op for op in ops if op.tag == abi.OP_NORM]
-        assert len(norms) == 6 + 5 + (1 if head != "none" else 0) and all(op.u.seq.buf[3] != abi.NO_BUF for op in norms[:11])
+        assert len(norms) == 6 + 5 and all(op.u.seq.buf[3] != abi.NO_BUF for op in norms)
+        assert [op.u.seq.buf[4] != abi.NO_BUF for op in norms] == [False] * 10 + [head != "none"]     # the final norm rides in the last residual step
         if head != "none":      # the head is the embedding table, capped in the product's epilogue
             assert ops[-1].tag == abi.OP_LINEAR and ops[-1].u.seq.n[6] == abi.ACTIVATIONS["softcap"] + 1 and ops[-1].u.seq.f[0] == 6.0 and ops[-1].u.seq.off[0] == m.arenas[-1].off["embed"]
         ext = [e.buf_idx for e in lp.program.externs]

@@ -306,10 +306,17 @@ class SetiraxModel:
         x = xs[0]
         ops.append(DeviceOp.embed(x, ctl, gl, GA.off["embed"], T, D, 1.0, wdt))
 
+        sublayers = sum(1 + (L["mlp"] is not None) for L in cfg.layers)
+        h = scratch("head.in", TD) if head != "none" else None
+
         def close(wb, w_off):      # x <- x + rms(y) w: the norm sits on the sublayer's result only
-            nonlocal x
+            nonlocal x, sublayers
             nx = new(TD) if keep_layers else (xs[1] if x == xs[0] else xs[0])
-            ops.append(DeviceOp.norm(nx, y, wb, w_off, T, D, eps, wdt, kind="rms", res=x))
+            sublayers -= 1
+            if sublayers == 0 and h is not None:      # the stack's last residual step and the model's final norm are one launch
+                ops.append(DeviceOp.norm(nx, y, wb, w_off, T, D, eps, wdt, kind="rms", res=x, then=h, then_w=gl, then_w_off=GA.off["final.norm"], then_kind="rms"))
+            else:
+                ops.append(DeviceOp.norm(nx, y, wb, w_off, T, D, eps, wdt, kind="rms", res=x))
             x = nx
 
         layer_bufs = []
@@ -393,8 +400,8 @@ class SetiraxModel:
         logits, rows = None, 0
         if head != "none":
             rows = T if head == "all" else 1
-            h = scratch("head.in", TD)
-            ops.append(DeviceOp.norm(h, x, gl, GA.off["final.norm"], T, D, eps, wdt, kind="rms"))
+            if not cfg.layers:
+                ops.append(DeviceOp.norm(h, x, gl, GA.off["final.norm"], T, D, eps, wdt, kind="rms"))
             logits = new(rows * cfg.vocab)
             cap = cfg.logit_softcap
             ops.append(DeviceOp.linear(logits, h, gl, GA.off["embed"], rows, cfg.vocab, D, wdt, src_off=0 if head == "all" else (T - 1) * D,
