@@ -147,6 +147,27 @@ def test_layer_streams_of_a_mixed_stack(cuda_backend):
     close(s)
 
 
+def test_shared_weights_with_constants_of_their_own(cuda_backend):
+    """Layers that run with another layer's tensors keep their own window, cap, scales, temperature and rotary schedule; a
+    reference may lead through a layer that itself shares weights, and may point forward."""
+    layers = [pair_layer(weights_of=2, window=12, base=500.0, scaling=None, mlp=dense()),
+              pair_layer(weights_of=0, window=3, softcap=0.0, tau=2.0, scale=0.5, left_scale=1.0, mlp=dense()),
+              pair_layer(mlp=dense()), latent_layer(mlp=dense()), latent_layer(weights_of=3, window=4, scale=0.9, mlp=dense())]
+    cfg = config(layers)
+    direct = copy.deepcopy(cfg)
+    direct["layers"][1]["weights_of"] = 2                   # what the chain 1 -> 0 -> 2 comes to
+    W = random_weights(cfg, seed=31, qk_gain=2.0)
+    toks = tokens(cfg, 40)
+    want, stream = forward(direct, W, toks)
+    s = open_model(cuda_backend, cfg, W, "float32", max_chunk=32, keep_layers=True)
+    got = np.concatenate([s.feed("a", toks[:32], range(32))] + [s.feed("a", [t], [0]) for t in toks[32:]])
+    layers_got = s.layer_streams(32, "all")
+    for i in range(len(layers)):
+        assert rel(layers_got[i], stream[i][:32]) < TOL, f"layer {i}"
+    assert rel(got, want) < TOL
+    close(s)
+
+
 # ── prefill against decoding, portions, first tokens ──
 @pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
 def test_prefill_equals_token_by_token(cuda_backend, dtype):

@@ -54,12 +54,28 @@ def test_config_errors():
                    lambda c: c["layers"][2]["mixer"].__setitem__("blocks", 5),                # width does not divide
                    lambda c: c["layers"][3].__setitem__("weights_of", 3),                     # itself
                    lambda c: c["layers"][3].__setitem__("weights_of", 1),                     # another kind of layer
-                   lambda c: c["layers"][4].__setitem__("weights_of", 3),                     # a layer without tensors of its own
+                   lambda c: c["layers"][3].__setitem__("weights_of", 9),                     # no such layer
+                   lambda c: c["layers"][3]["mixer"].__setitem__("kv_rank", 24),              # other tensor sizes than the layer whose weights it uses
+                   lambda c: (c["layers"][0].__setitem__("weights_of", 3), c["layers"][3].__setitem__("weights_of", 0)),     # a circle
                    lambda c: c["layers"][0]["mlp"].__setitem__("kind", "moe")):
         bad = json.loads(json.dumps(STACK))
         mutate(bad)
         with pytest.raises(ValueError):
             SetiraxConfig.from_dict(bad)
+
+
+def test_shared_weights_through_chains_with_constants_of_their_own():
+    """A reference may lead through another layer that shares weights, may point forward, and the layer keeps its own window, scale
+    and cap; only what sizes the tensors must agree."""
+    from zgml_b200.host.setirax import SetiraxConfig
+    c = json.loads(json.dumps(STACK))
+    c["layers"][4]["weights_of"] = 1
+    c["layers"].append(pair_layer(weights_of=4, window=3, softcap=0.0, tau=2.0, mlp=dense()))      # 6 -> 4 -> 1
+    del c["layers"][3]["weights_of"]
+    c["layers"][0]["weights_of"] = 3                                                                 # a reference forward: layer 0 runs with layer 3's tensors
+    cfg = SetiraxConfig.from_dict(c)
+    assert [L["weights"] for L in cfg.layers] == [3, 1, 2, 3, 1, 5, 1]
+    assert cfg.layers[6]["mixer"]["left"]["mask"]["size"] == 3 and cfg.layers[1]["mixer"]["left"]["mask"]["size"] == 7
 
 
 def test_state_and_lowering_shape(fake_device):
@@ -86,7 +102,7 @@ def test_state_and_lowering_shape(fake_device):
         assert tags.count(abi.OP_DELTA_RULE) == 2 and tags.count(abi.OP_ROTARY) == 0 and tags.count(abi.OP_RG_LRU) == 2 and tags.count(abi.OP_CAUSAL_CONV) == 2 + 2
         assert tags.count(abi.OP_ACTIVATION) == 0 and sum(op.tag == abi.OP_LINEAR and op.u.seq.n[6] == abi.ACTIVATIONS["relu2"] + 1 for op in ops) == 5
         app = [op for op in ops if op.tag == abi.OP_CACHE_APPEND]
-        assert [op.u.seq.n[10] for op in app] == [0, 6, 0, 6] and app[1].u.seq.buf[4] == app[3].u.seq.buf[4] != abi.NO_BUF      # rotary rides in the append, from one table
+        assert [op.u.seq.n[10] for op in app] == [0, 6, 0, 6] and abi.NO_BUF not in (app[1].u.seq.buf[4], app[3].u.seq.buf[4])      # rotary rides in the append, from the layer's table
         att = [op for op in ops if op.tag == abi.OP_CACHED_ATTENTION]
         assert [op.u.seq.buf[6] != abi.NO_BUF for op in att] == [True, False, True, False]       # sinks on the latent layers only
         assert [op.u.seq.f[1] for op in att] == [0.0, 5.0, 0.0, 5.0] and all(op.u.seq.off[3] == abi.MASK_WINDOW for op in att)
@@ -103,7 +119,7 @@ def test_state_and_lowering_shape(fake_device):
         if head != "none":      # the head is the embedding table, capped in the product's epilogue
             assert ops[-1].tag == abi.OP_LINEAR and ops[-1].u.seq.n[6] == abi.ACTIVATIONS["softcap"] + 1 and ops[-1].u.seq.f[0] == 6.0 and ops[-1].u.seq.off[0] == m.arenas[-1].off["embed"]
         ext = [e.buf_idx for e in lp.program.externs]
-        assert len(set(ext)) == len(ext) == 5 + 11 + 1                             # weight arenas + state buffers + one frequency table, each once
+        assert len(set(ext)) == len(ext) == 5 + 11 + 2                             # weight arenas + state buffers + a frequency table per turning layer, each once
 
 
 def test_layers_without_a_window_keep_every_position(fake_device):

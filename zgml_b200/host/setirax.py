@@ -66,6 +66,19 @@ def rotary_frequencies(rot: dict) -> np.ndarray:
     return f.astype(np.float32)
 
 
+def _tensor_sizes(kind: str, m: dict, mlp: Optional[dict]) -> tuple:
+    """What of a layer's entry sizes its tensors: two layers that share weights must agree on it (constants such as a window, a
+    scale or a cap may differ; each layer runs with its own)."""
+    if kind == "latent_attention":
+        t = (m["heads"], m["dim"], m["vdim"], m["kv_rank"])
+    elif kind == "parallel":
+        l, r = m["left"], m["right"]
+        t = (l["heads"], l["kv_heads"], l["dim"], l["vdim"], int(l.get("conv") or 0), r["heads"], r["dim"], r["vdim"])
+    else:
+        t = (m["width"], m["blocks"], int(m.get("conv") or 1))
+    return t + ((mlp.get("ff"),) if mlp else ())
+
+
 def _window(m: dict) -> Optional[int]:
     mask = m.get("mask")
     return int(mask["size"]) if mask else None
@@ -88,13 +101,16 @@ class SetiraxConfig:
             kind, m, mlp = L["type"], L["mixer"], L.get("mlp")
             if kind not in MIXERS:
                 raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
-            owner = L.get("weights_of", i)
-            if "weights_of" in L:
-                if not (0 <= owner < i) or "weights_of" in c["layers"][owner]:
-                    raise ValueError(f"layer {i}: weights_of must name an earlier layer with tensors of its own")
+            owner, seen = i, {i}
+            while "weights_of" in c["layers"][owner]:       # the layer whose tensors it runs with, through any chain of references
+                owner = c["layers"][owner]["weights_of"]
+                if not isinstance(owner, int) or not (0 <= owner < len(c["layers"])) or owner in seen:
+                    raise ValueError(f"layer {i}: weights_of must lead to a layer with tensors of its own")
+                seen.add(owner)
+            if owner != i:
                 o = c["layers"][owner]
-                if (o["type"], o["mixer"], o.get("mlp")) != (kind, m, mlp):
-                    raise ValueError(f"layer {i}: differs from layer {owner}, whose weights it uses")
+                if o["type"] != kind or (o.get("mlp") is None) != (mlp is None) or _tensor_sizes(kind, o["mixer"], o.get("mlp")) != _tensor_sizes(kind, m, mlp):
+                    raise ValueError(f"layer {i}: its sizes differ from layer {owner}'s, whose weights it uses")
             if kind == "latent_attention":
                 if min(m["heads"], m["dim"], m["vdim"], m["kv_rank"]) < 1:
                     raise ValueError(f"layer {i}: sizes must be positive")
@@ -188,10 +204,6 @@ class SetiraxModel:
                 A.add("a2.b", get(pr + "a2.b", (Hr * dr,)))
                 A.add("gla.norm", get(pr + "norm", (vr,)))
                 A.add("o", np.concatenate([get(pl + "o", (D, H * vdim)), get(pr + "o", (D, Hr * vr))], 1))    # one product = the sum of both branches
-                if l.get("rot"):
-                    f = rotary_frequencies(l["rot"])
-                    self._freqs[i] = DeviceBuffer(be, max(f.nbytes, 16), zero=False)
-                    self._freqs[i].upload(np.ascontiguousarray(np.concatenate([f, np.zeros(max(0, 4 - f.size), np.float32)])))
                 rq = C
                 meta.update(n_in=C + 2 * Hr * dr + 2 * Hr * vr + ra, C=C, taps=taps, rank_a=ra, rq=rq, rk=rq + Hr * dr, rv=rq + 2 * Hr * dr,
                             rg=rq + 2 * Hr * dr + Hr * vr, ra1=rq + 2 * Hr * dr + 2 * Hr * vr, mix=H * vdim + Hr * vr)
@@ -222,6 +234,12 @@ class SetiraxModel:
                 meta.update(ff=ff)
             self.layer_meta[i], self.arenas[i] = meta, A
             self.buffers[i] = A.upload(be)
+        for i, L in enumerate(cfg.layers):      # a frequency table per layer that turns its heads: the schedule is the layer's own constant
+            rot = L["mixer"]["left"].get("rot") if L["type"] == "parallel" else None
+            if rot:
+                f = rotary_frequencies(rot)
+                self._freqs[i] = DeviceBuffer(be, max(f.nbytes, 16), zero=False)
+                self._freqs[i].upload(np.ascontiguousarray(np.concatenate([f, np.zeros(max(0, 4 - f.size), np.float32)])))
         A = WeightArena(self.wdt)
         A.add("embed", get("embed", (cfg.vocab, D)))
         A.add("final.norm", get("final.norm", (D,)))
@@ -361,7 +379,7 @@ class SetiraxModel:
                 # query head turned and brought to unit RMS in place
                 ops.append(DeviceOp.cache_append(ext(cache), qkv, ctl, H * dim, 0, T, cw, qrs, cw, R, norm_w=wb, norm_off=A.off["unit"], normed=G * dim, eps=eps, wdt=wdt,
                                                  norm_group=dim, q_heads=H, q_col=0, q_norm_off=A.off["unit"], rot_layout="halves", head_rot=rot["dims"] if rot else 0,
-                                                 rot_base=rot["base"] if rot else 0.0, freqs=ext(self._freqs[owner]) if rot else None))
+                                                 rot_base=rot["base"] if rot else 0.0, freqs=ext(self._freqs[i]) if rot else None))
                 mw = meta["mix"]
                 mix = scratch("mix", T * mw)
                 ops.append(DeviceOp.cached_attention(mix, qkv, ext(cache), ext(cache), ctl, 0, 0, G * dim, T, H, G, 1, dim, vdim, qrs, cw, cw, R, l["scale"],
