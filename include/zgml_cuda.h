@@ -103,7 +103,10 @@ typedef enum ZgOpTag {
  *                   buf 0 dst 1 ctl 2 table | off 0 table 1 positions | n 0 T 1 D 2 wdt 3 positions | f 0 scale
  * LINEAR            dst[m, n] = act(sum_k src[m, k] W[n, k] (+ bias[n])); act (n6): 0 none, 1 + the ACTIVATION kind otherwise (f0: its
  *                   parameter, where the kind has one)
- *                   buf 0 dst 1 src 2 W 3 bias | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt 6 act
+ *                   buf 0 dst 1 src 2 W 3 bias 4 ctl | off 0 W 1 bias 2 src 3 dst | n 0 M 1 N 2 K 3 src row stride 4 dst row stride 5 wdt 6 act
+ *                   7 source slot stride
+ *                   With n7 > 0 the source rows are those of a per-sequence state buffer (a ring): n7 elements per slot, the slot
+ *                   from the control buffer buf 4.
  *                   f 0 activation parameter
  * NORM              dst = (res +) norm(src) * w ; kind bit 0 clear: (x - mean) / sqrt(var + eps), set: x / sqrt(mean(x^2) + eps);
  *                   kind bit 1: the weight is stored around zero and applied as (1 + w); kind bit 2: the result is also
@@ -213,7 +216,8 @@ typedef enum ZgOpTag {
  *                   off 0 q column 1 key column 2 value column (inside a cache row) 3 mask kind 4 mask size 5 weights 6 table row length
  *                   7 sinks
  *                   n 0 T 1 H 2 G 3 maps 4 dk 5 dv 6 q row stride 7 key row width 8 value row width 9 R 10 dst row stride
- *                   11 dst column 12 wdt of the sinks 13 output scale given | f 0 score scale 1 score cap 2 output scale
+ *                   11 dst column 12 wdt of the sinks 13 output scale given 14 caches without slots (rows the program itself computed
+ *                   for this step, position p in row p mod R as in a ring) | f 0 score scale 1 score cap 2 output scale
  * MAP_COMBINE       differential attention's combination of two maps: o = a[.., 0, :] - f0 * a[.., 1, :], then
  *                   o / sqrt(mean(o^2) + f1) * f2 per (token, head)
  *                   buf 0 dst [rows, dv] 1 src [rows, 2, dv] | n 0 rows 1 dv | f 0 lambda 1 eps 2 output scale

@@ -336,6 +336,36 @@ def test_long_windows_and_split_decoding(cuda_backend, layer):
     close(s)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_steps_expand_the_latent(cuda_backend, dtype):
+    """Steps of 128 tokens run a latent layer in the expanded form: keys and values per head from one product over the ring's rows of
+    the sequence's slot, then multi-head attention over them.  Sharp softmaxes, sinks, a ring of 99 + 128 rows that wraps, the second
+    slot (after a request that left other latents there), steps that start anywhere; the shorter steps and single tokens that follow
+    run absorbed over the same ring.  The float32 session is made to expand too, so the comparison is exact."""
+    cfg = config([latent_layer(heads=3, dim=16, vdim=24, rank=64, window=100, mlp=dense()), lru_layer(), latent_layer(heads=3, dim=16, vdim=24, rank=64, window=100, weights_of=0, mlp=dense())],
+                 width=64, vocab=50)
+    W = random_weights(cfg, seed=29, qk_gain=4.0)
+    n = 470
+    toks = tokens(cfg, n)
+    want, _ = forward(cfg, W, toks)
+    s = open_model(cuda_backend, cfg, W, dtype, n_slots=2, max_chunk=128)
+    s.model.expand_float32 = True
+    s.feed("first", toks[:3], [])                            # takes slot 0 and keeps it
+    s.feed("other", toks[50:300], [])                        # leaves its latents in slot 1
+    s.release("other")
+    got = np.concatenate([s.feed("a", toks[:5], range(5)), s.feed("a", toks[5:460], range(455))] + [s.feed("a", [t], [0]) for t in toks[460:]])   # 4 + 1, then 128 x 3 + 64 + 4 + 2 + 1
+    assert s.pool.slot("a") == 1
+    tags = [op.tag for op in s.program(128, "all")[0].program.ops]
+    from zgml_b200 import abi
+    assert tags.count(abi.OP_HEAD_LINEAR) == 1 and abi.OP_HEAD_LINEAR in [op.tag for op in s.program(64, "all")[0].program.ops]      # only the recurrent block's gates are left at 128
+    if dtype == "float32":
+        assert rel(got, want) < TOL
+    else:
+        err = np.max(np.abs(got - want), axis=1) / np.max(np.abs(want))
+        assert np.median(err) < 3e-2 and np.mean(err < 6e-2) > 0.9
+    close(s)
+
+
 def test_long_steps_walk_segments_side_by_side(cuda_backend):
     """Steps of 256 tokens: the recurrent unit cuts them into 64 segments walked side by side and the gated linear attention
     takes its prepared walk; the states they leave must carry on into smaller steps and single tokens, in a slot that is not the

@@ -212,10 +212,11 @@ class DeviceOp:
         return DeviceOp._seq(abi.OP_EMBED, [dst, ctl, table], [table_off, positions_off or 0], [T, D, wdt, int(positions_off is not None)], [scale])
 
     @staticmethod
-    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0, act=None, act_param=0.0):
-        """`act`: an activation of abi.ACTIVATIONS applied in the epilogue, after the bias (`act_param`: its parameter, where it has one)."""
-        return DeviceOp._seq(abi.OP_LINEAR, [dst, src, w, bias], [w_off, bias_off, src_off, dst_off],
-                             [M, N, K, src_rs or K, dst_rs or N, wdt, 0 if act is None else abi.ACTIVATIONS[act] + 1], [act_param])
+    def linear(dst, src, w, w_off, M, N, K, wdt, bias=None, bias_off=0, src_off=0, dst_off=0, src_rs=0, dst_rs=0, act=None, act_param=0.0, ctl=None, src_slot_stride=0):
+        """`act`: an activation of abi.ACTIVATIONS applied in the epilogue, after the bias (`act_param`: its parameter, where it has one).
+        `src_slot_stride` > 0: the source rows are the slot's part of a per-sequence state buffer (that many elements per slot; slot from `ctl`)."""
+        return DeviceOp._seq(abi.OP_LINEAR, [dst, src, w, bias, ctl if src_slot_stride else None], [w_off, bias_off, src_off, dst_off],
+                             [M, N, K, src_rs or K, dst_rs or N, wdt, 0 if act is None else abi.ACTIVATIONS[act] + 1, src_slot_stride], [act_param])
 
     @staticmethod
     def norm(dst, src, w, w_off, rows, cols, eps, wdt, kind="layer", res=None, then=None, then_w=None, then_w_off=0, then_kind="layer",
@@ -323,15 +324,15 @@ class DeviceOp:
     @staticmethod
     def cached_attention(dst, q, k_cache, v_cache, ctl, q_col, k_col, v_col, T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, scale,
                          mask="causal", mask_size=0, weights="softmax", score_table=None, table_len=0, softcap=0.0, sink=None, sink_off=0, sink_wdt=0,
-                         out_scale=None, dst_rs=0, dst_col=0):
-        """`score_table`: an f32 buffer [H * maps, table_len] added to the scaled scores by distance; `weights` "sigmoid": every
+                         out_scale=None, dst_rs=0, dst_col=0, unslotted=False):
+        """`unslotted`: the caches are rows the program computed for this step (no state slots).  `score_table`: an f32 buffer [H * maps, table_len] added to the scaled scores by distance; `weights` "sigmoid": every
         visible key weighs sigmoid(score), not normalised over the keys.  `softcap` > 0: the scaled score passes cap * tanh(s / cap).
         `sink`: a weight buffer with one learned score per (head, map) at `sink_off` whose exponential joins the softmax's denominator.
         `out_scale` multiplies the result, which may land at column `dst_col` of rows `dst_rs` wide."""
         kinds = {"causal": abi.MASK_CAUSAL, "window": abi.MASK_WINDOW, "block": abi.MASK_BLOCK}
         return DeviceOp._seq(abi.OP_CACHED_ATTENTION, [dst, q, k_cache, v_cache, ctl, score_table, sink],
                              [q_col, k_col, v_col, kinds[mask], mask_size, {"softmax": abi.WEIGHTS_SOFTMAX, "sigmoid": abi.WEIGHTS_SIGMOID}[weights], table_len, sink_off],
-                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, dst_rs, dst_col, sink_wdt, int(out_scale is not None)], [scale, softcap, out_scale or 0.0])
+                             [T, H, G, maps, dk, dv, q_rs, k_width, v_width, rows, dst_rs, dst_col, sink_wdt, int(out_scale is not None), int(unslotted)], [scale, softcap, out_scale or 0.0])
 
     @staticmethod
     def map_combine(dst, src, rows, dv, lam, eps, out_scale):

@@ -71,7 +71,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
 }
 
 // f32 rows -> dense bf16 [Mp][Kp] (zero padding), two k per thread
-__global__ void k_to_bf16(const float* __restrict__ x, uint32_t x_rs, uint32_t* __restrict__ out, uint32_t kp2, uint32_t M, uint32_t K) {
+// (ctl: the rows are those of a per-sequence state buffer, `slot_stride` elements per slot; the slot is the control word's)
+__global__ void k_to_bf16(const float* __restrict__ x, uint32_t x_rs, uint32_t* __restrict__ out, uint32_t kp2, uint32_t M, uint32_t K, const float* __restrict__ ctl,
+                          uint32_t slot_stride) {
+    if (ctl) x += (size_t)reinterpret_cast<const int*>(ctl)[ZG_CTL_SLOT] * slot_stride;
     const uint32_t m = blockIdx.y;
     for (uint32_t k2 = blockIdx.x * blockDim.x + threadIdx.x; k2 < kp2; k2 += gridDim.x * blockDim.x) {
         const uint32_t k = 2 * k2;
@@ -267,11 +270,11 @@ unsigned int zg_dense_gemm_timeouts() {
 }
 
 bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float* src, float* dst, uint32_t M, uint32_t N, uint32_t K,
-                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act, float act_p) {
+                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act, float act_p, const float* ctl, uint32_t slot_stride) {
     if (!prepare()) return false;
     const uint32_t Kp = (K + BK - 1) / BK * BK, Mp = (M + BM - 1) / BM * BM;
     uint32_t* xb = reinterpret_cast<uint32_t*>(scratch);
-    k_to_bf16<<<dim3((Kp / 2 + 255) / 256, Mp), 256, 0, st>>>(src, src_rs, xb, Kp / 2, M, K);
+    k_to_bf16<<<dim3((Kp / 2 + 255) / 256, Mp), 256, 0, st>>>(src, src_rs, xb, Kp / 2, M, K, ctl, slot_stride);
     ZG_COUNT_LAUNCH();
     CUtensorMap map_a, map_b;
     const cuuint32_t estr[2] = {1, 1};

@@ -168,7 +168,9 @@ struct CaArgs {
     uint32_t sink_bf16;    // its weight type
     float out_scale;       // the result is multiplied by it
     uint32_t dst_rs;       // row stride of dst (its first column is folded into the pointer)
+    uint32_t unslotted;    // the caches belong to the step (rows recomputed by the program), not to a state slot
 };
+__device__ __forceinline__ uint32_t ca_slot(const CaArgs& a) { return a.unslotted ? 0u : (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT); }
 __device__ __forceinline__ float ca_score(const CaArgs& a, float dot) {
     const float s = dot * a.scale;
     return a.cap > 0.0f ? a.cap * tanhf(s / a.cap) : s;
@@ -193,7 +195,7 @@ __global__ void k_cached_attention(CaArgs a) {
     const uint32_t item = blockIdx.x * nw + warp;
     if (item >= a.T * HM) return;
     const uint32_t t = item / HM, hm = item % HM, h = hm / a.maps, m = hm % a.maps, g = h / (a.H / a.G);
-    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
+    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = ca_slot(a);
     const uint32_t p = pos0 + t, lo = mask_low(p, a.kind, a.size);
     float* q = sq + warp * a.dk;
     const float* qrow = a.q + (size_t)t * a.q_rs + a.q_off + (size_t)hm * a.dk;
@@ -281,7 +283,7 @@ __global__ void __launch_bounds__(kCtThreads) k_cached_attention_tiled(CaArgs a,
     const uint32_t n_vs = (a.dv + DV - 1) / DV;
     const uint32_t tile = n_tiles - 1 - blockIdx.x;    // later rows walk more keys: heaviest first
     const uint32_t gm = blockIdx.y / n_vs, vs = blockIdx.y % n_vs, g = gm / a.maps, m = gm % a.maps;
-    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
+    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = ca_slot(a);
     const uint32_t total = a.T * rh, r0 = tile * kCtBQ, nq = min((uint32_t)kCtBQ, total - r0);
     const uint32_t p_min = pos0 + r0 / rh, p_max = pos0 + (r0 + nq - 1) / rh;
     const uint32_t k_lo = mask_low(p_min, a.kind, a.size);
@@ -499,7 +501,7 @@ __global__ void __launch_bounds__(kCfThreads) k_cached_attention_few(CaArgs a, u
     const uint32_t tid = threadIdx.x, row = tid >> 4, kq = tid & 15;
     const uint32_t warp = tid >> 5, rg = (tid & 31) >> 3, kg = tid & 7;
     const uint32_t gm = blockIdx.x, g = gm / a.maps, m = gm % a.maps;
-    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = (uint32_t)ctl_word(a.ctl, ZG_CTL_SLOT);
+    const uint32_t pos0 = (uint32_t)ctl_word(a.ctl, ZG_CTL_POS), slot = ca_slot(a);
     const uint32_t total = a.T * rh, p_max = pos0 + a.T - 1;
     const uint32_t k_lo = mask_low(pos0, a.kind, a.size);
     const uint32_t n_keys = p_max - k_lo + 1, per = (n_keys + splits - 1) / splits;
@@ -876,7 +878,7 @@ bool zg_mix_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (R < T) return fail("cached_attention: cache rows");   // the caller sizes R for what the mask reaches and bounds the positions
             if (s.off[0] + H * maps * dk > qrs || s.off[1] + G * maps * dk > kw || s.off[2] + G * dv > vw) return fail("cached_attention: columns");
             const size_t drs = s.n[10] ? s.n[10] : H * maps * dv;
-            if (s.n[11] + H * maps * dv > drs || s.f[1] < 0.0f || s.n[13] > 1) return fail("cached_attention: destination columns, cap or output scale");
+            if (s.n[11] + H * maps * dv > drs || s.f[1] < 0.0f || s.n[13] > 1 || s.n[14] > 1) return fail("cached_attention: destination columns, cap or output scale");
             if (s.buf[6] != ZG_NO_BUF && (s.off[5] || !wfits(6, s.n[12], s.off[7], H * maps))) return fail("cached_attention: sinks");
             if (!fits(0, 0, (T - 1) * drs + s.n[11] + H * maps * dv) || !fits(1, 0, (T - 1) * qrs + s.off[0] + H * maps * dk) || !have(2) || elems[s.buf[2]] < R * kw || !have(3) ||
                 elems[s.buf[3]] < R * vw || !fits(4, 0, ZG_CTL_IDS))
@@ -973,7 +975,7 @@ bool zg_launch_mix_op(const ZgOp& op, float* const* bufs, float* scratch, cudaSt
             a.kw = s.n[7]; a.k_off = s.off[1]; a.vw = s.n[8]; a.v_off = s.off[2]; a.R = s.n[9]; a.kind = s.off[3]; a.size = s.off[4]; a.scale = s.f[0];
             a.tab = s.buf[5] != ZG_NO_BUF ? bufs[s.buf[5]] : nullptr; a.tab_rs = s.off[6]; a.wkind = s.off[5];
             a.cap = s.f[1]; a.out_scale = s.n[13] ? s.f[2] : 1.0f; a.dst_rs = s.n[10] ? s.n[10] : a.H * a.maps * a.dv; a.dst += s.n[11];
-            a.sink = nullptr; a.sink_bf16 = s.n[12] == ZG_W_BF16;
+            a.sink = nullptr; a.sink_bf16 = s.n[12] == ZG_W_BF16; a.unslotted = s.n[14];
             if (s.buf[6] != ZG_NO_BUF) a.sink = a.sink_bf16 ? (const void*)wptr<bf16>(bufs, s.buf[6], s.off[7]) : (const void*)wptr<float>(bufs, s.buf[6], s.off[7]);
             const bool aligned = ca_aligned(s) && ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.kc) | reinterpret_cast<uintptr_t>(a.vc)) & 15) == 0;
             if (aligned && ca_few(s)) {

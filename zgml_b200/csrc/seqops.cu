@@ -32,8 +32,10 @@ __global__ void k_embed(float* __restrict__ dst, const float* __restrict__ ctl, 
 constexpr int kGemvRows = 8;
 template <typename WT>
 __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
-                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act, float act_p) {
+                              uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act, float act_p, const float* __restrict__ ctl,
+                              uint32_t slot_stride) {
     pdl_enter();
+    if (ctl) src += (size_t)ctl_word(ctl, ZG_CTL_SLOT) * slot_stride;      // the rows of a per-sequence state buffer
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (n >= N) return;
     const WT* w = W + (size_t)n * K;
@@ -59,7 +61,8 @@ __global__ void k_linear_rows(float* __restrict__ dst, const float* __restrict__
 // vectors per lane are in flight per trip.
 template <typename WT, int MR>
 __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W, const WT* __restrict__ bias,
-                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act, float act_p) {
+                                  uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs, uint32_t dst_rs, uint32_t act, float act_p, const float* __restrict__ ctl,
+                                  uint32_t slot_stride) {
     // Weights are constants of the model, so this warp's weight row is pulled toward L2 BEFORE the wait on the predecessor:
     // in a replayed graph the HBM stream of a matvec starts under the tail of the kernel that produces its input.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -74,6 +77,7 @@ __global__ void k_linear_rows_vec(float* __restrict__ dst, const float* __restri
     asm volatile("griddepcontrol.wait;" ::: "memory");
     constexpr int V = WVec<WT>::n;
     extern __shared__ float xs[];                      // [M][K]
+    if (ctl) src += (size_t)ctl_word(ctl, ZG_CTL_SLOT) * slot_stride;
     for (uint32_t e = threadIdx.x; e < M * K; e += blockDim.x) xs[e] = src[(size_t)(e / K) * src_rs + e % K];
     __syncthreads();
     const uint32_t n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -134,9 +138,10 @@ constexpr int kTM = 64, kTN = 64, kTK = 16;
 template <typename WT>
 __global__ void __launch_bounds__(256) k_linear_tile(float* __restrict__ dst, const float* __restrict__ src, const WT* __restrict__ W,
                                                      const WT* __restrict__ bias, uint32_t M, uint32_t N, uint32_t K, uint32_t src_rs,
-                                                     uint32_t dst_rs, uint32_t act, float act_p) {
+                                                     uint32_t dst_rs, uint32_t act, float act_p, const float* __restrict__ ctl, uint32_t slot_stride) {
     __shared__ float As[kTK][kTM + 4];
     __shared__ float Ws[kTK][kTN + 4];
+    if (ctl) src += (size_t)ctl_word(ctl, ZG_CTL_SLOT) * slot_stride;
     const uint32_t m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
     const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // outputs: rows ty * 4 + i, columns tx * 4 + j
     float acc[4][4] = {};
@@ -1435,6 +1440,7 @@ bool zg_seq_op_valid(const ZgOp& op, const size_t* elems, size_t n_bufs, char* w
             if (s.buf[3] != ZG_NO_BUF && !wfits(3, s.off[1], N)) return fail("linear: bias extent");
             if (s.buf[0] == s.buf[1]) return fail("linear: in place");
             if (s.n[6] > 5 || (s.n[6] == 5 && !(s.f[0] > 0.0f))) return fail("linear: activation");
+            if (s.n[7] && (s.n[7] < s.off[2] + (M - 1) * srs + K || !fits(4, 0, ZG_CTL_IDS))) return fail("linear: source slots");
             return true;
         }
         case ZG_OP_NORM: {
@@ -1564,9 +1570,10 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
             float* dst = bufs[s.buf[0]] + s.off[3];
             const float* src = bufs[s.buf[1]] + s.off[2];
             const bool has_bias = s.buf[3] != ZG_NO_BUF;
+            const float* slot_ctl = s.n[7] ? (const float*)bufs[s.buf[4]] : (const float*)nullptr;      // the source is the slot's part of a state buffer
             if (scratch && zg_seq_op_scratch_elems(op, bufs))
                 return zg_dense_gemm_launch(wptr<bf16>(bufs, s.buf[2], s.off[0]), has_bias ? wptr<bf16>(bufs, s.buf[3], s.off[1]) : nullptr, src, dst, M, N, K,
-                                            s.n[3], s.n[4], scratch, st, s.n[6], s.f[0]);
+                                            s.n[3], s.n[4], scratch, st, s.n[6], s.f[0], slot_ctl, s.n[7]);
             ZG_SEQ_WDT(s.n[5], {
                 const WT* W = wptr<WT>(bufs, s.buf[2], s.off[0]);
                 const WT* b = has_bias ? wptr<WT>(bufs, s.buf[3], s.off[1]) : nullptr;
@@ -1575,13 +1582,13 @@ bool zg_launch_seq_op(ZgCudaCtx* ctx, const ZgOp& op, float* const* bufs, float*
                     const size_t xs_bytes = (size_t)M * K * sizeof(float);
                     const bool vec = K % V == 0 && (reinterpret_cast<size_t>(W) & 15) == 0 && xs_bytes <= 48 * 1024;
                     const dim3 grid((N + 7) / 8);
-                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
-                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
-                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
-                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
+                    if (vec && M == 1) launch_pdl(k_linear_rows_vec<WT, 1>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0], slot_ctl, s.n[7]);
+                    else if (vec && M <= 4) launch_pdl(k_linear_rows_vec<WT, 4>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0], slot_ctl, s.n[7]);
+                    else if (vec) launch_pdl(k_linear_rows_vec<WT, 8>, dim3(grid), dim3(256), xs_bytes, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0], slot_ctl, s.n[7]);
+                    else launch_pdl(k_linear_rows<WT>, dim3(grid), dim3(256), 0, st, dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0], slot_ctl, s.n[7]);
                 } else {
                     const dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
-                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0]);
+                    k_linear_tile<WT><<<grid, 256, 0, st>>>(dst, src, W, b, M, N, K, s.n[3], s.n[4], s.n[6], s.f[0], slot_ctl, s.n[7]);
                 }
             });
             ZG_SEQ_CHECK();

@@ -391,4 +391,4 @@ size_t zg_rec_op_scratch_elems(const ZgOp& op);   // shared scratch of a long SS
 bool zg_launch_rec_op(const ZgOp& op, float* const* bufs, float* scratch, cudaStream_t st);
 size_t zg_seq_op_operand_scratch(const ZgOp& op);   // f32 slots an op's own scratch operand needs (MOE_FFN)
 bool zg_dense_gemm_launch(const void* w_bf16, const void* bias_bf16, const float* src, float* dst, uint32_t M, uint32_t N, uint32_t K,
-                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act = 0, float act_p = 0.0f);   // act: 0 none, 1 + ACTIVATION kind
+                          uint32_t src_rs, uint32_t dst_rs, float* scratch, cudaStream_t st, uint32_t act = 0, float act_p = 0.0f, const float* ctl = nullptr, uint32_t slot_stride = 0);   // act: 0 none, 1 + ACTIVATION kind

@@ -16,10 +16,12 @@ This file is the model's configuration reader, its weight packer and its LOWERIN
 sequence-model DeviceOps of the CUDA library (csrc/seqops.cu, csrc/mixops.cu, csrc/recops.cu) and all state in the session's
 `SequenceStatePool`.  Every size and per-model constant comes from config.json or a tensor's shape.
 
-latent      [q | dkv] = W x in ONE matmul; CACHE_APPEND norms the latent on its way into the ring; the attention runs ABSORBED:
+latent      [q | dkv] = W x in ONE matmul; CACHE_APPEND norms the latent on its way into the ring.  Short steps run ABSORBED:
             q' = W_uk^T q per head (HEAD_LINEAR), CACHED_ATTENTION of q' over the latent itself (one key head that is also the
             value, window mask, sinks), then W_uv per head (HEAD_LINEAR) and W_o.  Scores (W_uk^T q) . c = q . (W_uk c) are the
-            same numbers in another order of summation; nothing per head is cached.
+            same numbers in another order of summation.  Long steps of bfloat16 sessions run EXPANDED: one tensor-core product
+            turns every row of the sequence's ring into keys | values per head (program scratch, recomputed by each such step),
+            and ordinary multi-head attention runs over them.  Only the latent is ever cached.
 pair        [q | k | v | q' | k' | v' | g | a1] = W x in ONE matmul for both branches.  Left: CAUSAL_CONV over q | k | v, CACHE_APPEND
             (every key head turned by its rotary position — frequencies from a table evaluated at load — then brought to unit RMS on
             its way into the ring, values copied, query heads turned and normed in place), CACHED_ATTENTION (cap, window) writing left_scale * heads into the left
@@ -48,6 +50,7 @@ ARCHITECTURE = "Setirax"
 DEFAULT_CONTEXT = 4096     # positions a sequence may reach when a layer attends without a window and the caller names no bound
 MIXERS = ("latent_attention", "parallel", "rglru")
 LRU_RATE = 8.0             # log a = -8 r softplus(lam): fixed by the design
+EXPAND_MIN_TOKENS = 128    # steps from this size on expand a latent layer's keys and values per head (bfloat16 sessions)
 
 
 def rotary_frequencies(rot: dict) -> np.ndarray:
@@ -155,6 +158,7 @@ class SetiraxModel:
         self.arenas: Dict[int, WeightArena] = {}
         self.buffers: Dict[int, DeviceBuffer] = {}
         self._freqs: Dict[int, DeviceBuffer] = {}
+        self.expand_float32 = False      # float32 sessions keep latent layers absorbed; set before the first long step to run them expanded as well
         # a layer that attends without a window caches every position: the session then bounds the sequence
         self.bounded_context = any(_window(L["mixer"] if L["type"] == "latent_attention" else L["mixer"]["left"]) is None
                                    for L in cfg.layers if L["type"] != "rglru")
@@ -180,6 +184,7 @@ class SetiraxModel:
                 uk, uv = get(p + "mix.uk", (H * dim, rank)), get(p + "mix.uv", (H * vdim, rank))
                 A.add("ukT", uk.reshape(H, dim, rank).transpose(0, 2, 1))     # [H, rank, dim]: q' = W_uk^T q per head
                 A.add("uv", uv)                                               # [H, vdim, rank] as stored
+                A.add("ukv", np.concatenate([uk, uv], 0))                     # long steps expand keys | values of the ring's rows in one product
                 meta["sink"] = has(p + "mix.sink")
                 if meta["sink"]:
                     A.add("sink", get(p + "mix.sink", (H,)))
@@ -288,6 +293,14 @@ class SetiraxModel:
                 specs.append(StateSpec(f"l{i}.lru", m["width"], True))
         return specs
 
+    def _expands(self, T: int, R: int, m: dict) -> bool:
+        """Whether a step of T tokens runs a latent layer in the expanded form.  Expanding costs 2 R rank H (dim + vdim) FLOPs on the
+        tensor cores per step; the absorbed form costs (2 rank - dim - vdim) more multiply-adds per (query, key, head) in f32.  Worth it
+        for long steps of bfloat16 sessions whose latent fits the tensor-core product (rank a multiple of 8, at least 64); float32
+        sessions, whose products are exact f32 tiles either way, and short steps stay absorbed."""
+        rank, per_head = m["kv_rank"], m["dim"] + m["vdim"]
+        return (self.wdt == abi.W_BF16 or self.expand_float32) and T >= EXPAND_MIN_TOKENS and rank % 8 == 0 and rank >= 64 and 2 * rank > per_head
+
     # ── lowering ──
     def lower(self, T: int, head: str, pool: SequenceStatePool, keep_layers: bool = False) -> LoweredProgram:
         cfg, wdt, D, eps = self.cfg, self.wdt, self.cfg.width, self.cfg.norm_eps
@@ -350,14 +363,23 @@ class SetiraxModel:
                 cache = pool.buffers[f"l{i}.latent"]
                 R = cache.elems // (slots * rank)
                 ops.append(DeviceOp.cache_append(ext(cache), proj, ctl, H * dim, 0, T, rank, ni, rank, R, norm_w=wb, norm_off=A.off["dkv.norm"], normed=rank, eps=eps, wdt=wdt))
-                qa = scratch("qa", T * H * rank)
-                ops.append(DeviceOp.head_linear(qa, proj, wb, A.off["ukT"], T, H, rank, dim, wdt, src_hs=dim, src_rs=ni))
-                ctx = scratch("ctx", T * H * rank)
-                ops.append(DeviceOp.cached_attention(ctx, qa, ext(cache), ext(cache), ctl, 0, 0, 0, T, H, 1, 1, rank, rank, H * rank, rank, rank, R, m["scale"],
-                                                     mask="causal" if window is None else "window", mask_size=window or 0,
-                                                     sink=wb if meta["sink"] else None, sink_off=A.off.get("sink", 0), sink_wdt=wdt))
                 att = scratch("att", T * H * vdim)
-                ops.append(DeviceOp.head_linear(att, ctx, wb, A.off["uv"], T, H, vdim, rank, wdt))
+                sink = dict(sink=wb if meta["sink"] else None, sink_off=A.off.get("sink", 0), sink_wdt=wdt)
+                mask = dict(mask="causal" if window is None else "window", mask_size=window or 0)
+                if self._expands(T, R, m):
+                    # EXPANDED form: keys | values of every ring row per head from ONE tensor-core product over the slot's latents, then
+                    # ordinary multi-head attention over them: dim + vdim numbers per (query, key, head) instead of 2 rank
+                    kvw = H * (dim + vdim)
+                    kv = scratch("latent.kv", R * kvw)
+                    ops.append(DeviceOp.linear(kv, ext(cache), wb, A.off["ukv"], R, kvw, rank, wdt, ctl=ctl, src_slot_stride=R * rank))
+                    ops.append(DeviceOp.cached_attention(att, proj, kv, kv, ctl, 0, 0, H * dim, T, H, H, 1, dim, vdim, ni, kvw, kvw, R, m["scale"], unslotted=True, **mask, **sink))
+                else:
+                    # ABSORBED form: q' = W_uk^T q per head, attention of q' over the latent itself (one key head that is also the value), W_uv per head
+                    qa = scratch("qa", T * H * rank)
+                    ops.append(DeviceOp.head_linear(qa, proj, wb, A.off["ukT"], T, H, rank, dim, wdt, src_hs=dim, src_rs=ni))
+                    ctx = scratch("ctx", T * H * rank)
+                    ops.append(DeviceOp.cached_attention(ctx, qa, ext(cache), ext(cache), ctl, 0, 0, 0, T, H, 1, 1, rank, rank, H * rank, rank, rank, R, m["scale"], **mask, **sink))
+                    ops.append(DeviceOp.head_linear(att, ctx, wb, A.off["uv"], T, H, vdim, rank, wdt))
                 ops.append(DeviceOp.linear(y, att, wb, A.off["o"], T, D, H * vdim, wdt))
             elif L["type"] == "parallel":
                 l, r = m["left"], m["right"]
