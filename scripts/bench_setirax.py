@@ -43,7 +43,7 @@ def setirax_arm(be, size, prefill_T, context, reps):
     D = cfg.width
     active = state = 0          # weights / ring and state elements one decoded token touches
     attn_flops = walk_flops = 0  # f32 work of the prefill chunk that is not a matmul
-    expand_flops = 0             # tensor-core work of the expanded latent layers (per step, whatever its length)
+    expand_flops = absorbed_only = 0   # tensor-core work of the expanded latent layers (per step, whatever its length); weights only the absorbed form multiplies
     for i, L in enumerate(cfg.layers):
         m, meta = L["mixer"], model.layer_meta[L["weights"]]
         if L["type"] == "latent_attention":
@@ -52,7 +52,9 @@ def setirax_arm(be, size, prefill_T, context, reps):
             state += min(w, context) * rk
             expanded = model._expands(prefill_T, w - 1 + prefill_T, m)      # long bfloat16 steps: keys | values per head from a tensor-core product
             attn_flops += 2 * H * ((d + dv) if expanded else 2 * rk) * prefill_T * min(w, prefill_T / 2)
-            expand_flops += 2 * (w - 1 + prefill_T) * rk * H * (d + dv) * prefill_T // prefill_T if expanded else 0
+            if expanded:      # the per-head products of the absorbed form are not run; the ring's rows are expanded once per step instead
+                expand_flops += 2 * (w - 1 + prefill_T) * rk * H * (d + dv)
+                absorbed_only += H * rk * (d + dv)
         elif L["type"] == "parallel":
             l, rt = m["left"], m["right"]
             w = l["mask"]["size"]
@@ -74,7 +76,7 @@ def setirax_arm(be, size, prefill_T, context, reps):
     handle = s.program(prefill_T, "last")[1]
     dev = timed(lambda: be.lib.zg_cuda_execute_device(be.ctx, handle.ptr), be.sync, reps)
     out["prefill"] = {"tokens": prefill_T, "tok_s_e2e": round(prefill_T / e2e), "tok_s_device": round(prefill_T / dev), "ms_device": round(dev * 1e3, 3),
-                      "matmul_tflops_device": round((2.0 * (body * prefill_T + cfg.vocab * D) + expand_flops) / dev / 1e12, 1), "attention_gflop_f32": round(attn_flops / 1e9, 1),
+                      "matmul_tflops_device": round((2.0 * ((body - absorbed_only) * prefill_T + cfg.vocab * D) + expand_flops) / dev / 1e12, 1), "attention_gflop_f32": round(attn_flops / 1e9, 1),
                       "walk_gflop_f32": round(walk_flops / 1e9, 1), "kernels": be.program_stats(handle)["kernels"],
                       "tensor_core_linears": be.program_stats(handle)["tensor_core_linears"]}
     s.feed("d", prompt, [])
