@@ -4,7 +4,7 @@
  *
  * TEST INFRASTRUCTURE ONLY.  Nothing under oracle/ is part of the product: only
  * tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / --impl reference
- * legs may build, load or call it, and only as the checker / timed CPU baseline.
+ * legs may build, load or call it, and only as the comparison oracle / timed CPU baseline.
  *
  * Parity pinning: the reference (Zig >= 0.16) cannot be built in this image
  * (no zig toolchain; its W8A8 kernel is aarch64-only inline asm,

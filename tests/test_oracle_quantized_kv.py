@@ -3,7 +3,7 @@ QuantizedKVCache / attentionQuantized (src/quant.zig:1259-1620) re-run against t
 
 They are property tests against an in-test float reference with stated tolerances; inputs come from
 std.Random.DefaultPrng in the reference — any RNG re-runs them, here numpy U(-1, 1) like
-fillRandF32 (src/quant.zig:1253-1257).  CPU only: the oracle is the checker the GPU tests compare against."""
+fillRandF32 (src/quant.zig:1253-1257).  CPU only: the oracle is what the GPU tests compare against."""
 import numpy as np
 import pytest
 

@@ -465,14 +465,14 @@ def synthetic_config(width: int, n_layers: int, heads: int, kv_heads: int, dim: 
         if kind == "latent_attention":
             mixer = {"heads": heads, "dim": dim, "vdim": dim, "kv_rank": kv_rank, "mask": {"size": window}, "scale": dim ** -0.5}
         elif kind == "parallel":
-            left = {"conv": conv, "dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": window}, "scale": 8.0 / dim, "softcap": 20.0, "vdim": dim,
-                    "rot": {"base": 10000.0, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
-            right = {"dim": dim, "heads": gla_heads or max(1, heads // 2), "tau": 16.0, "vdim": dim}
+            left = {"conv": conv, "dim": dim, "heads": heads, "kv_heads": kv_heads, "mask": {"size": window}, "scale": 8.0 / dim, "softcap": 50.0, "vdim": dim,
+                    "rot": {"base": 10000.0, "dims": dim, "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 4096}}}
+            right = {"dim": dim, "heads": gla_heads or max(1, heads // 2), "tau": 8.0, "vdim": dim}
             mixer = {"left": left, "left_scale": 0.5, "right": right, "right_scale": 0.5}
         else:
             mixer = {"blocks": lru_blocks or heads, "conv": conv, "width": lru_width or width}
         layers.append({"type": kind, "mixer": mixer, "mlp": None if kind == "rglru" else {"kind": "dense", "ff": ff}})
-    return {"architecture": ARCHITECTURE, "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": layers}
+    return {"architecture": ARCHITECTURE, "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 50.0, "layers": layers}
 
 
 def synthetic_tensors(cfg: dict, seed: int = 0, decay_rank: int = 64):
