@@ -327,7 +327,7 @@ k_allreduce_peer(float* __restrict__ buf, uint32_t n2, const ZgPeerComm pc) {
 // bare = rmsnorm(sum), gamma_rep = gamma, norm = bare * gamma_rep (ZgNormMacro, one row) — in ONE launch.  Each of the 16 CTAs
 // reduces its slice exactly as k_allreduce_peer does, keeps going on the slice, and the sum of squares of the whole row is
 // exchanged through 16 local {partial, epoch} cells (8-byte volatile stores, polled; added in CTA order -> identical on
-// every CTA and every rank).  One kernel boundary less on the critical path of every all-reduce — and MEASURED SLOWER (round 2,
+// every CTA and every rank).  One kernel boundary less on the critical path of every all-reduce — and MEASURED SLOWER (in a
 // same box A/B of the 80-layer 70B decode: 2 GPUs 131.0 -> 128.5 tok/s, 8 GPUs 191.8 -> 187.3): the separate norm kernel is
 // resident and has its operands' addresses ready when the all-reduce ends (programmatic dependent launch), while here every
 // CTA waits for the slowest CTA's peers and then for an L2 round trip of the partial exchange.  Off by default (ZG_CUDA_AR_NORM=1).

@@ -1,5 +1,5 @@
 // The prefill quantized matmul of qgemm.cu as a CTA-PAIR kernel: tcgen05.mma.cta_group::2, one 256 x 256 output tile per
-// cluster of two CTAs.  Default for M > 128 since round 2 (parity tests green with it, 427 / 458 / 457 TFLOP/s against
+// cluster of two CTAs.  Default for M > 128 (parity tests green with it, 427 / 458 / 457 TFLOP/s against
 // 384 / 404 / 411 for the 1-CTA tile at M = 2048 on the Llama-3-8B linears); ZG_GEMM_CTA2=0 falls back to the 1-CTA tile.
 //
 // Why (profiles/r01_qgemm_ncu_full_stall_summary.txt): the 1-CTA 128 x 256 tile is bound by shared-memory

@@ -196,7 +196,7 @@ qgemv_kernel(const __grid_constant__ QGemvBatchT<PRO != 0> bt) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         for (uint32_t i = 0; i < NS && pf_left; i++) issue_chunk();
     }
-    // Measured and rejected (round 2): pulling the REST of the warp's weight run into L2 here with cp.async.bulk.prefetch.L2
+    // Measured and rejected: pulling the REST of the warp's weight run into L2 here with cp.async.bulk.prefetch.L2
     // (the kernel sits resident 5-11 us before its activations exist) made every configuration slower — 70B shard of 8:
     // 61.2 -> 62.1 us/layer, unsharded 175 -> 198, GEMV microbenchmark 5.79 -> 5.24 TB/s: the wait is not idle HBM time.
     // the constant ones plane (digit index 3) of every (record, row): B column of ones -> sum_k q
@@ -907,7 +907,7 @@ ZgGemvPlan zg_qgemv_plan(const ZgCudaCtx* ctx, const ZgCudaQWeight* w, uint32_t 
     // Wave quantisation: `count` matvecs share the launch, and a launch of slightly more CTAs than the GPU holds at once
     // (Llama-3-70B gate|up sharded over 8 GPUs: 2 x 112 column groups x 2 splits = 448 CTAs for 444 slots) costs an
     // extra round.  ZG_GEMV_WAVE=1 tries a few more k-splits and takes the cheapest in rounds x (records per warp + fixed
-    // per-CTA cost).  MEASURED AND REJECTED as a default (round 2, same box A/B): 2 % slower on the 70B decode step both
+    // per-CTA cost).  MEASURED AND REJECTED as a default (same box A/B): 2 % slower on the 70B decode step both
     // unsharded (252.4 -> 247.2 tok/s at 24 layers) and for an 8-way shard (58.9 -> 60.5 us/layer) — every extra split adds
     // a partial-sum round trip through global scratch that costs more than the emptier last round saves.
     static const bool wave_aware = [] { const char* e = getenv("ZG_GEMV_WAVE"); return e && e[0] == '1'; }();

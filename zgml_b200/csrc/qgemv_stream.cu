@@ -3,7 +3,7 @@
 //   dst[n] = sum_k ( x[k] * s[(k*N + n) / 32] ) * q[k, n]        (QuantizedWeight.matmul, src/quant.zig:475-578, M == 1)
 //
 // Same arithmetic as qgemv_kernel (digit planes of c = s * x on the integer tensor cores, see qgemv.cu), different
-// work decomposition.  Measured on the Llama-3-70B matvecs (ncu, round 2): the k-split kernel spends as many issue
+// work decomposition.  Measured on the Llama-3-70B matvecs (ncu): the k-split kernel spends as many issue
 // slots on the per-column-group flush / CTA reduction / split arrival as on streaming, and a launch of 360 equal CTAs
 // for 444 resident slots leaves SMs with 3 CTAs running 1.4x longer than SMs with 2.  Here
 //
