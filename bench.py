@@ -16,7 +16,7 @@ Two legs per run, ONE JSON line:
   4096x14336}) x (int8+f32 scale, Q8_0-origin, Q4_0-origin), one batch-1 matvec over EACH of R distinct GPU-resident
   weight copies (R x bytes >= 512 MB > 4 x L2: every weight byte comes from HBM).  `roofline` is its dominant kernel —
   qgemv_kernel, the kernel that also dominates the decode step — against MEASURED_PEAKS.json hbm_gbs.
-  Algorithmic bytes per GEMV = (K*N/32)*B_blk + 4K + 4N, B_blk = 36 / 34 / 18 (SURVEY.md §8d).
+  Algorithmic bytes per GEMV = (K*N/32)*B_blk + 4K + 4N, B_blk = 36 / 34 / 18.
 
 `cpu_baseline` / `--impl reference`: the oracle executor (reference semantics, oracle/zgml_oracle.c) decoding the same
 70B-shape model on the host cores — a bounded sample: 1- and 2-layer models at full width with the full LM head, per-token
@@ -39,7 +39,7 @@ sys.path.insert(0, ROOT)
 
 SHAPES = [(4096, 4096), (4096, 14336)]          # (K, N): zgml rows=K, cols=N
 FORMATS = [("i8_f32", 36), ("q8_0", 34), ("q4_0", 18)]
-if os.environ.get("ZG_BENCH_SHAPES"):            # kernel-tuning sweeps only (not the judged workload)
+if os.environ.get("ZG_BENCH_SHAPES"):            # kernel-tuning sweeps only (not the default workload)
     SHAPES = [tuple(int(v) for v in t.split("x")) for t in os.environ["ZG_BENCH_SHAPES"].split(",")]
 if os.environ.get("ZG_BENCH_FORMATS"):
     FORMATS = [f for f in FORMATS if f[0] in os.environ["ZG_BENCH_FORMATS"].split(",")]
@@ -56,7 +56,7 @@ def alg_bytes(K, N, blk):
 
 
 def host_weight(K, N, fmt, seed):
-    """Synthetic weight in the reference's host form (i8 data + f32 scales, bs=32), SURVEY §8d config 2."""
+    """Synthetic weight in the reference's host form (i8 data + f32 scales, bs=32), the quantized-GEMM configuration of the bench."""
     r = np.random.default_rng(seed)
     if fmt == "q4_0":
         data = r.integers(-8, 8, K * N, dtype=np.int8)
@@ -696,7 +696,7 @@ def run_extras(be, torch):
         out["decode_smollm_1p7b_q4_0_ctx512"] = {"tok_s": round(n / dt, 1), "device_tok_s": round(n / dd, 1), "ms_per_token_device": round(1e3 * dd / n, 3),
                                                  "hbm_bytes_per_token": int(qb), "frac_of_hbm_floor": round(qb / (peak * 1e9) / (dd / n), 4),
                                                  "kernels_per_token": be.program_stats(sess.handle)["kernels"]}
-        # SURVEY 8f-4: the tied f32 LM head as an argmax-safe f16 copy (zg_cuda_program_promote_dense), same greedy tokens
+        # the tied f32 LM head as an argmax-safe f16 copy (zg_cuda_program_promote_dense), same greedy tokens
         toks_f32 = []
         sess.pos = 512
         t = 1
@@ -769,7 +769,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=5.0, help="budget of the GEMV leg's single-thread CPU sample")
     ap.add_argument("--cpu-tokens", type=int, default=3, help="decode tokens per sample model in cpu_baseline")
     ap.add_argument("--gemv-steps", type=int, default=20, help="passes over the GEMV microbench set (its own leg, not `steps`)")
-    ap.add_argument("--decode-layers", type=int, default=0, help="override the 80 layers of the decode model (experiments only; the judged run uses 80)")
+    ap.add_argument("--decode-layers", type=int, default=0, help="override the 80 layers of the decode model (experiments only; the default run uses 80)")
     ap.add_argument("--no-check", action="store_true", help="skip the 2-layer oracle comparison")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extras", action="store_true")

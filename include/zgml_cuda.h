@@ -46,7 +46,7 @@ typedef enum ZgOpTag {
     ZG_OP_ATTENTION = 10,
     ZG_OP_FUSED_ELEMENTWISE = 11,
     ZG_OP_COUNT = 12,
-    /* Extensions (no zgml counterpart: the reference has no distributed layer, SURVEY.md §8e).  Emitted only by
+    /* Extensions (no zgml counterpart: the reference has no distributed layer).  Emitted only by
      * the sharded session of this repo; need zg_cuda_comm_init().  One NCCL collective each, in program order. */
     ZG_OP_ALLREDUCE = 12, /* buf[offset .. offset + n) = sum over ranks, in place */
     ZG_OP_ALLGATHER = 13, /* dst[dst_offset + r * n ..) = rank r's src[src_offset .. + n), every rank */
@@ -361,7 +361,7 @@ typedef struct ZgQWeight {
     size_t rows, cols, block_size;
 } ZgQWeight;
 
-/* Extension (SURVEY.md §8f-3, direct GGUF->device upload): a descriptor with block_size == ZG_QWEIGHT_RESIDENT
+/* Extension (direct GGUF->device upload): a descriptor with block_size == ZG_QWEIGHT_RESIDENT
  * refers to a weight already packed in HBM — `data` is the ZgCudaQWeight* that zg_cuda_qweight_upload /
  * zg_cuda_qweight_upload_gguf returned, rows/cols must match it, the other fields are ignored.  The program
  * borrows it (the caller frees it after zg_cuda_free).  Lets a loader stream a model into HBM one tensor at a
@@ -538,7 +538,7 @@ int zg_cuda_quantize_input_host(ZgCudaCtx* ctx, const float* h_input, size_t K, 
 int zg_cuda_gemv_w8a8_device(ZgCudaCtx* ctx, const ZgCudaQWeight* w, const float* d_input, float* d_dst);
 int zg_cuda_gemv_w8a8_host(ZgCudaCtx* ctx, const ZgCudaQWeight* w, const float* h_input, float* h_dst);
 
-/* Quantized KV cache + attention over it (SURVEY.md §8f-2) — reference src/quant.zig:633-1091, callers
+/* Quantized KV cache + attention over it — reference src/quant.zig:633-1091, callers
  * src/llama_inference.zig:330-377.  Column-major Q8 cache: column c = d_head int8 + d_head / block_size f32 scales; one
  * column per kv position inside a head's slab.  d_head <= 512 and d_head % block_size == 0 as in the reference; this
  * implementation additionally needs d_head % 4 == 0 and block_size % 4 == 0. */
@@ -577,7 +577,7 @@ int zg_cuda_attention_quantized_host(ZgCudaCtx* ctx, float* h_dst, size_t dst_co
  * Returns 0 on success; -1 (program unchanged) when the program's cache accesses are not whole d_head columns. */
 int zg_cuda_program_quantize_kv(ZgCudaCtx* ctx, ZgCudaProgram* prog, size_t block_size, int int8_query);
 
-/* Format hint for dense matmul operands (SURVEY.md 8f-4; precedent: the WGPU backend's f16 promotion of matmul B buffers that
+/* Format hint for dense matmul operands (precedent: the WGPU backend's f16 promotion of matmul B buffers that
  * have initial uploads, src/backend/wgpu.zig:1068-1106).  Every matmul op of the program with M == 1 and a k-contiguous B
  * operand that no op writes (the tied LM head x @ token_embed^T, src/models/llama.zig:162-165) gets a 16-bit copy of that operand;
  * the op then streams the copy (half the bytes), bounds each output's error by ||x|| * ||w - round16(w)|| and recomputes every

@@ -9,8 +9,8 @@
  * Parity pinning: the reference (Zig >= 0.16) cannot be built in this image
  * (no zig toolchain; its W8A8 kernel is aarch64-only inline asm,
  * src/quant.zig:347-354), so this restatement is pinned against every
- * known-answer vector the reference's own tests hold for the path (SURVEY.md
- * §8c; tests/test_oracle_golden.py).  End-to-end GGUF-direct LLaMA logits are
+ * known-answer vector the reference's own tests hold for the path
+ * (tests/test_oracle_golden.py).  End-to-end GGUF-direct LLaMA logits are
  * not pinned by any reference test ("parity unpinned" for configs 1/3/4/5 beyond
  * the per-op vectors).
  *
@@ -207,7 +207,7 @@ ZO_API int zo_gemv_pool(const int8_t* t_d, const float* t_s, const float* input,
     return (int)(n_disp + 1);
 }
 
-/* ── QuantizedKVCache + attentionQuantized — src/quant.zig:633-1091 (SURVEY.md §8f-2) ─────────
+/* ── QuantizedKVCache + attentionQuantized — src/quant.zig:633-1091 ─────────
  * Column-major Q8 cache: column c = d_head int8 at q_data[c*d_head], d_head/bs scales at
  * scales[c*bpc].  storeColumn = quantizeInput on the column (src/quant.zig:689-701). */
 ZO_API void zo_kv_store_column(int8_t* q_data, float* scales, size_t d_head, size_t bs, size_t col,

@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Quantized KV cache inside programs (zg_cuda_program_quantize_kv): attention GB/s against the algorithmic bytes of
-SURVEY.md §8f-2 — 2 * seq_kv * (d_head + 4 * d_head / bs) per head and decode step — next to the f32 cache, and SmolLM-1.7B
+2 * seq_kv * (d_head + 4 * d_head / bs) per head and decode step — next to the f32 cache, and SmolLM-1.7B
 Q4_0 decode tok/s with the mode on / off at 512 and 2040 tokens of context."""
 import json
 import os

@@ -1,4 +1,4 @@
-"""bf16 LM-head matvec with the argmax-safe exact recompute (csrc/dense_head.cu, zg_cuda_program_promote_dense; SURVEY.md §8f-4,
+"""bf16 LM-head matvec with the argmax-safe exact recompute (csrc/dense_head.cu, zg_cuda_program_promote_dense;
 precedent src/backend/wgpu.zig:1068-1106).  Bars: the argmax and the winning logit are the unpromoted program's, bit for bit;
 every other logit within 2e-4 (f16) / 2e-3 (bf16) of the output scale — f16 stays inside the 1e-3 whole-program logit budget; non-finite activations behave like the
 exact path; an input that overwrites the operand refreshes the copy."""

@@ -346,7 +346,7 @@ def test_prefill_rows_match_decode_rows(cuda_backend):
     w.free()
 
 
-# ── QuantizedWeight.fromSlice / matmulBias on device (SURVEY.md §8a rows a2, a7) ────────────────
+# ── QuantizedWeight.fromSlice / matmulBias on device ────────────────
 @pytest.mark.parametrize("K,N,bs", [(64, 64, 32), (100, 37, 32), (576, 1536, 32), (128, 96, 64), (33, 7, 16), (4096, 512, 128)])
 def test_from_slice_on_device_is_bit_identical_to_reference(cuda_backend, K, N, bs):
     r = rng(K * 7 + N + bs)

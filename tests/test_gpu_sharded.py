@@ -1,4 +1,4 @@
-"""Row-sharded decode on real GPUs (SURVEY.md §8e) and the resident-weight extension.
+"""Row-sharded decode on real GPUs and the resident-weight extension.
 
 * 1 GPU: a program built from weights streamed into HBM first (ZG_QWEIGHT_RESIDENT descriptors) equals the program
   that uploads the same weights through compile_program; collective ops at world 1 are identity / copy.

@@ -85,7 +85,7 @@ def test_smollm_1p7b_width_q4_0_decode_at_context_512_matches_oracle(cuda_backen
 @pytest.mark.parametrize("case", ["outliers", "scale-spread", "both"])
 def test_matvec_adversarial_activations_and_scales(cuda_backend, fmt, case):
     """Heavy-tailed activations (a few 1e3 x outliers per row) and per-block scales spanning three decades inside every column
-    group (ADVICE r1): the decode matvec quantises x * s to a 2^-23 grid relative to max|x| * max(s) of a warp's k-range
+    group: the decode matvec quantises x * s to a 2^-23 grid relative to max|x| * max(s) of a warp's k-range
     (csrc/qgemv.cu), so its error is bounded by that product, not by the individual terms.  Checked per element:
     |delta| <= 1e-3 |want| + 2^-22 max|x| smax sum_k |q[k, n]|  (the analytic worst case: half a grid step per term), 1e-3
     relative on every output that is at least 5 % of the row maximum, and the usual 1e-3 on the row maximum."""

@@ -16,13 +16,13 @@ def test_program_structure_matches_reference_lowering():
     assert tags.count(abi.OP_QMATMUL) == 7 * TINY.n_layers          # q,k,v,o,gate,up,down (llama_transformer.zig:204-206,240,130-132)
     assert tags.count(abi.OP_ATTENTION) == TINY.n_heads * TINY.n_layers
     assert tags.count(abi.OP_ROPE) == (TINY.n_heads + TINY.n_kv_heads) * TINY.n_layers
-    assert tags.count(abi.OP_MATMUL) == 1                           # tied LM head stays dense f32 (SURVEY fact 10)
+    assert tags.count(abi.OP_MATMUL) == 1                           # tied LM head stays dense f32
     assert len(lp.slice_assign_ops) == 2 * TINY.n_kv_heads * TINY.n_layers
     for i in lp.slice_assign_ops:
         assert lp.program.ops[i].u.slice_assign.patch_stride == TINY.d_head
     assert lp.n_qmatmul == len(lp.program.qweights)
     shapes = linear_shapes(SMOLLM_135M)
-    assert sum(k * n for k, n in shapes.values()) * SMOLLM_135M.n_layers == 106_168_320  # SURVEY §8: 106.2 M quantized weights
+    assert sum(k * n for k, n in shapes.values()) * SMOLLM_135M.n_layers == 106_168_320  # 106.2 M quantized weights
 
 
 def test_rope_table_matches_reference_formula():

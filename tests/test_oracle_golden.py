@@ -1,5 +1,5 @@
 """Pin the CPU oracle against every known-answer vector the reference's own tests hold
-for the quantized path (SURVEY.md §8c).  CPU only."""
+for the quantized path.  CPU only."""
 import math
 import struct
 

@@ -1,8 +1,8 @@
-"""Oracle pinning for the quantized KV cache path (SURVEY.md §8f-2): the reference's own tests for
+"""Oracle pinning for the quantized KV cache path: the reference's own tests for
 QuantizedKVCache / attentionQuantized (src/quant.zig:1259-1620) re-run against the C restatement.
 
 They are property tests against an in-test float reference with stated tolerances; inputs come from
-std.Random.DefaultPrng in the reference — any RNG re-runs them (SURVEY.md §8c), here numpy U(-1, 1) like
+std.Random.DefaultPrng in the reference — any RNG re-runs them, here numpy U(-1, 1) like
 fillRandF32 (src/quant.zig:1253-1257).  CPU only: the oracle is what the GPU tests compare against."""
 import numpy as np
 import pytest

@@ -1,4 +1,4 @@
-"""Row-sharded LLaMA decode (SURVEY.md §8e) on the CPU, world_size 2 over gloo: every rank lowers its shard
+"""Row-sharded LLaMA decode on the CPU, world_size 2 over gloo: every rank lowers its shard
 (zgml_b200/host/llama.py `shard_weights` + `build_program`), the oracle executor runs the ops and gloo the
 collectives.  The sharded logits must equal the unsharded oracle run on the same weights (the all-reduce only
 regroups the k-sum: 1e-5 relative), greedy tokens identical."""

@@ -175,7 +175,7 @@ class DeviceOp:
         o._steps_keepalive = arr  # the caller owns `steps` (src/device_inference.zig:291-298)
         return o
 
-    # Multi-GPU extensions (no zgml counterpart; SURVEY.md §8e).  One NCCL collective each.
+    # Multi-GPU extensions (no zgml counterpart).  One NCCL collective each.
     @staticmethod
     def allreduce(buf, n, offset=0):
         o = DeviceOp._mk(abi.OP_ALLREDUCE)

@@ -1,4 +1,4 @@
-// NCCL collectives for row-sharded linear layers (SURVEY.md §8e): one process per GPU, one communicator per
+// NCCL collectives for row-sharded linear layers: one process per GPU, one communicator per
 // context, collectives enqueued on the program's stream (captured into its CUDA graph like any kernel).
 // libnccl is resolved with dlopen at first use, so single-GPU users need no NCCL at all.
 //

@@ -1,4 +1,4 @@
-// Dense LM-head matvec with 16-bit weights (f16 or bf16) and an argmax-safe bound (SURVEY.md §8f-4; opt-in, zg_cuda_program_promote_dense).
+// Dense LM-head matvec with 16-bit weights (f16 or bf16) and an argmax-safe bound (opt-in, zg_cuda_program_promote_dense).
 //
 // The tied LM head of the SmolLM / Llama models is a dense f32 matmul of one activation row against token_embed^T
 // (src/models/llama.zig:162-165): [vocab, d_model] f32, the largest single byte stream of a SmolLM decode step.  The

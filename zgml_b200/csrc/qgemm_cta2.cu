@@ -2,7 +2,7 @@
 // cluster of two CTAs.  Default for M > 128 (parity tests green with it, 427 / 458 / 457 TFLOP/s against
 // 384 / 404 / 411 for the 1-CTA tile at M = 2048 on the Llama-3-8B linears); ZG_GEMM_CTA2=0 falls back to the 1-CTA tile.
 //
-// Why (profiles/r01_qgemm_ncu_full_stall_summary.txt): the 1-CTA 128 x 256 tile is bound by shared-memory
+// Why (measured with ncu's stall counters): the 1-CTA 128 x 256 tile is bound by shared-memory
 // bandwidth — every 128 x 256 x 16 MMA reads 12 KB of operands in its 128 cycles, and the dequantized weight tile has to be
 // stored through the same pipe: 1152 + 512 + 256 = 1920 wavefronts per 64-k stage against 1536 cycles of MMA.  In a CTA pair
 // each CTA holds its own 128 activation rows and only HALF of the weight tile (128 columns); the pair's MMA (M = 256,

@@ -21,7 +21,7 @@
 //    weights on the integer tensor-core path (IMMA).  A column of ones in B yields
 //    sum_k q[k, n], which removes the digit bias.  Integer accumulation is exact; the
 //    only rounding beyond the reference's is the 2^-23 fixed-point grid of c relative
-//    to max|x| * max(s) of the warp's k-range (see DESIGN.md).
+//    to max|x| * max(s) of the warp's k-range.
 //  * int4 weights stay packed: byte = 16 u[n+8] + u[n] (u = q + 8) is fed to the
 //    MMA as one u8 operand row next to the row u[n] = byte & 15; the two results
 //    separate exactly ((X - Y) / 16), and the +8 bias is removed with per-digit sums.

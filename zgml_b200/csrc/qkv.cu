@@ -1,5 +1,5 @@
 // Quantized KV cache and attention over it for sm_100a — zgml's QuantizedKVCache / attentionQuantized
-// (src/quant.zig:633-1091; callers src/llama_inference.zig:330-377), SURVEY.md §8f-2.
+// (src/quant.zig:633-1091; callers src/llama_inference.zig:330-377).
 //
 //   * Cache layout as the reference's: column-major Q8, column c = d_head int8 at q[c * d_head] plus d_head / bs f32
 //     scales at s[c * bpc]; one column per (kv position) inside a head's slab of n_cols.  3.6x fewer bytes than the f32

@@ -8,7 +8,7 @@ Mirror of zgml's reader, same names and error behaviour:
     — src/models/gguf_loader.zig:99-154,171-204,214-236,340-391 (tensor names :258-283).
   * `upload_quantized_tensor`, `load_resident` — what changes for the device: the raw Q8_0 / Q4_0 block bytes of
     `get_tensor_data` go straight to `zg_cuda_qweight_upload_gguf` (expanded and repacked on the GPU), one tensor at a
-    time; the host never holds the 1.125 B / weight int8 expansion that `quantizedWeightFromInfo` makes (SURVEY.md §8f-3).
+    time; the host never holds the 1.125 B / weight int8 expansion that `quantizedWeightFromInfo` makes.
   * `GGUFWriter`, `write_llama_gguf` — our tool for the synthetic random-init models of BASELINE.json's configs, in zgml's
     convention (2-D linears `dims = [K, N]`, blocks over the flat `[K, N]` array; `token_embd.weight` `[d_model, vocab]`).
 
@@ -427,7 +427,7 @@ _COLUMN_SHARDED = ("wq", "wk", "wv", "w_gate", "w_up", "out_proj")   # this rank
 def shard_blocks(info: TensorInfo, raw: np.ndarray, key: str, rank: int, world: int):
     """This rank's slab of a Q8_0 / Q4_0 [K, N] tensor, cut at BLOCK level from the raw GGUF bytes (no int8 expansion).
     Blocks run along n inside one k row (flat index k * N + n), so a column slab [n0, n1) with n0, n1 multiples of 32 is
-    the block range [n0 / 32, n1 / 32) of every row, and a row slab is one contiguous run (SURVEY.md §8e).
+    the block range [n0 / 32, n1 / 32) of every row, and a row slab is one contiguous run.
     Returns (bytes, K_local, N_local); the same slabs as `llama.shard_weights` makes from the expanded form."""
     K, N = info.dims[0], info.dims[1]
     bb = info.type_.type_size
@@ -460,7 +460,7 @@ def upload_quantized_tensor(be, gf: GGUFFile, name: str, key: str = "", rank: in
 def load_resident(be, gf: GGUFFile, cfg: Optional[LlamaConfig] = None, rank: int = 0, world: int = 1):
     """The device form of loadDirectQuantized: linears go tensor by tensor from the (memory-mapped) file into HBM and
     the program borrows them (`ZG_QWEIGHT_RESIDENT`).  With world > 1 every rank reads only its own slabs of the file
-    (row-sharded model, SURVEY.md §8e).  Returns (LlamaWeights, handles to free after the session)."""
+    (row-sharded model).  Returns (LlamaWeights, handles to free after the session)."""
     cfg = cfg or config_from_gguf(gf)
     check_shardable(cfg, world)
     shapes = linear_shapes(cfg)
@@ -484,7 +484,7 @@ def load_resident(be, gf: GGUFFile, cfg: Optional[LlamaConfig] = None, rank: int
 
 
 def write_llama_gguf(path: str, cfg: LlamaConfig, kind: str = "q8_0", seed: int = 0, embed_scale: float = 0.05, version: int = 3):
-    """A random-init GGUF of `cfg`'s architecture in zgml's convention (SURVEY.md §8d): linears Q8_0 / Q4_0 with
+    """A random-init GGUF of `cfg`'s architecture in zgml's convention: linears Q8_0 / Q4_0 with
     `dims = [K, N]`, norms = 1 (f32), `token_embd.weight` f32 `[d_model, vocab]` ~ U(-embed_scale, embed_scale)."""
     from .llama import synthetic_gguf_blocks
     t = GGMLType.q8_0 if kind == "q8_0" else GGMLType.q4_0

@@ -81,7 +81,7 @@ class LlamaWeights:
     norm2: List[np.ndarray]
     norm_f: np.ndarray
     out_proj: Optional[QuantizedWeightUpload] = None   # untied LM head [d_model, vocab]
-    # Row-sharded form (SURVEY.md §8e): `shard = (rank, world)`; every linear then holds only this rank's slab
+    # Row-sharded form: `shard = (rank, world)`; every linear then holds only this rank's slab
     # (see `shard_weights`), `head_rows` the rank's vocab rows of the tied embedding.  token_embed stays whole
     # (host-side row lookup); anything indexable by token id works.
     shard: Optional[tuple] = None
@@ -100,7 +100,7 @@ def rope_tables(cfg: LlamaConfig):
 
 
 def check_shardable(cfg: LlamaConfig, world: int):
-    """Slab boundaries must fall on multiples of 32 so that no quant block is split (SURVEY.md §8e)."""
+    """Slab boundaries must fall on multiples of 32 so that no quant block is split."""
     if world == 1:
         return
     if cfg.n_heads % world or cfg.n_kv_heads % world:
@@ -177,7 +177,7 @@ class LlamaProgram:
 
 
 def build_program(cfg: LlamaConfig, w: LlamaWeights, token_len: int = 1) -> LlamaProgram:
-    """Unsharded (w.shard is None): the reference lowering.  Sharded over `world` GPUs (SURVEY.md §8e): q/k/v/gate/up
+    """Unsharded (w.shard is None): the reference lowering.  Sharded over `world` GPUs: q/k/v/gate/up
     hold this rank's output columns (its heads, its slice of d_ff), wo/down this rank's input rows followed by an
     all-reduce of the d_model partial sums, the LM head this rank's vocab slice followed by an all-gather of the
     last position's logits.  Activations are replicated; the KV cache is sharded by KV head."""
@@ -269,7 +269,7 @@ def build_program(cfg: LlamaConfig, w: LlamaWeights, token_len: int = 1) -> Llam
     rms(norm, x, gf, bare, gamma_rep)
     logits = B.new(V * T)
     if cfg.tied_lm_head:
-        # x.matMul(false, token_embed, true) (models/llama.zig:162-165): dense f32, never quantized (SURVEY fact 10)
+        # x.matMul(false, token_embed, true) (models/llama.zig:162-165): dense f32, never quantized
         emb = B.new(V * D, w.head_rows if w.shard else w.token_embed)
         ops.append(DeviceOp.matmul(logits, norm, emb, T, V, D, D, 1, 1, D, dst_row_stride=V))
     else:
@@ -374,7 +374,7 @@ class _OpsView:
 
 
 def synthetic_weights(cfg: LlamaConfig, kind: str = "q8_0", seed: int = 0, embed_scale: float = 0.05) -> LlamaWeights:
-    """Random-init GGUF-direct weights in the reference's host form (SURVEY.md §8d config 1/3): per linear
+    """Random-init GGUF-direct weights in the reference's host form: per linear
     q ~ U{-127..127} (q8_0) / U{-8..7} (q4_0), one f16-representable scale per 32 flat elements sized so the
     dequantized weight is ~U(-b, b) with b = sqrt(6 / K) (kaimingUniform, src/nn.zig:91-105); norms = 1;
     token embedding ~U(-embed_scale, embed_scale)."""

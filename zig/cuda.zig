@@ -6,7 +6,7 @@
 //! `zg_cuda_*` C entry points, the same way src/backend/metal.zig wraps metal_shim.h.
 //! It contains no arithmetic and no fallbacks.
 //!
-//! NOT compiled in this repository's CI: the build image has no zig toolchain (DESIGN.md §1).
+//! NOT compiled in this repository's CI: the build image has no zig toolchain.
 //! The C-ABI it binds is exercised through the identical ctypes binding in zgml_b200/abi.py.
 //!
 //! build.zig additions:   exe.linkSystemLibrary("zgml_cuda"); exe.addLibraryPath(.{ .cwd_relative = "<repo>/zgml_b200/lib" });
